@@ -12,8 +12,10 @@ of parts are registered by name (`register_architecture`, `parts.registry`).
 """
 from .config.base import ConfigError
 from .config.gemma2 import Gemma2Config
+from .config.sigalorn import SigalornConfig
 from .registry import architectures, register_architecture, resolve, unregister_architecture
 from .models import gemma2 as _gemma2            # registers Gemma2ForCausalLM
+from .models import sigalorn as _sigalorn        # registers Sigalorn
 from .engine.engine import Engine, build_model, from_config, load, open, write_random_model
 from .engine.step import StepEntry, StepError
 from .engine.generate import Reply

@@ -9,7 +9,7 @@ cache line, and fixed-size state per sequence.
   fixed shape per sequence).
 * Lines with the same need form a *group* with storage of its own.  A KV group
   is a pool of pages of PAGE tokens, `[lines, pages, kv heads, PAGE, head size]`
-  for keys and the same for values, and a page table `[slots, pages per sequence]`
+  for keys and the same for values (with the values' own head size where a mixer's differs), and a page table `[slots, pages per sequence]`
   shared by the group's lines (a sequence has the same length in all of them).
   A windowed group is a ring: position p lives at p mod ring, ring = the window
   rounded up to whole pages, so a sequence never holds more than ring / PAGE
@@ -51,6 +51,11 @@ class KVNeed:
     n_kv_heads: int
     head_dim: int
     window: int | None = None      # None: every position is kept
+    v_head_dim: int | None = None  # size of a value head when it differs from the keys' (None: head_dim)
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim else self.head_dim
 
 
 @dataclass(frozen=True)
@@ -113,9 +118,8 @@ class KVGroup:
         self.pool = PagePool(n_pages)
         self.table_host = np.zeros((n_slots, self.pages_per_seq), dtype=np.int32)
         self.table = torch.zeros((n_slots, self.pages_per_seq), dtype=torch.int32, device=device)
-        shape = (len(lines), n_pages, need.n_kv_heads, PAGE, need.head_dim)
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.k = torch.zeros((len(lines), n_pages, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
+        self.v = torch.zeros((len(lines), n_pages, need.n_kv_heads, PAGE, need.value_dim), dtype=dtype, device=device)
         self.held: dict[int, list[int]] = {}
         self.dirty = False
 
@@ -149,7 +153,7 @@ class KVGroup:
             self.dirty = False
 
     def bytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class StateGroup:
@@ -251,9 +255,10 @@ class ModelCache:
         item = torch.empty((), dtype=dtype).element_size()
         sizes = []
         for need, lines in kv_lines.items():
-            b = 2 * len(lines) * group_pages[need] * need.n_kv_heads * PAGE * need.head_dim * item
+            b = len(lines) * group_pages[need] * need.n_kv_heads * PAGE * (need.head_dim + need.value_dim) * item
             kind = f"window {need.window}" if need.window else "all positions"
-            sizes.append((f"{len(lines)} lines of {need.n_kv_heads} x {need.head_dim} keys and values, {kind}", b))
+            width = f"{need.head_dim}" if need.value_dim == need.head_dim else f"({need.head_dim} + {need.value_dim})"
+            sizes.append((f"{len(lines)} lines of {need.n_kv_heads} x {width} keys and values, {kind}", b))
         for need, lines in st_lines.items():
             n = 1
             for d in need.shape:

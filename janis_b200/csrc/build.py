@@ -1,8 +1,10 @@
 """Compiling the CUDA sources for sm_100a and loading them.
 
-There are two kinds of library: `core` (norms, embedding, rotary encoding and
-cache write, the 32-bit product, the skinny bfloat16 product, sampling) and one
-`attention` library per head size, compiled with that size as a constant.  A
+There are three kinds of library: `core` (norms, embedding, rotary encoding and
+cache write, the 32-bit product, the skinny bfloat16 product, sampling), one
+`attention` library per head size, compiled with that size as a constant, and
+`mixers` (attention whose heads are mixed before the softmax, with values of a
+size of their own; gated linear attention), whose sizes are run-time numbers.  A
 library is compiled the first time it is asked for, so a process compiles what
 its model needs and nothing else; the file name carries a hash of the sources
 and flags, so a stale library is never loaded.  The kernels are plain C entry
@@ -33,6 +35,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "gemm_tc05.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_prefill_tc05.cu", "attention_no_alloc.cu"]
+MIXER_SOURCES = ["attention_talk.cu", "linear_attention.cu"]
 HEADERS = ["common.cuh", "attention_no_alloc.h", "attention_prefill_tiles.cuh"]
 
 
@@ -181,9 +184,14 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     return _load(f"janis_attn_hd{head_dim}{tag}", ATTENTION_SOURCES, [f"JANIS_HEAD_DIM={head_dim}", *extra])
 
 
+def mixers_library() -> ctypes.CDLL:
+    return _load("janis_mixers", MIXER_SOURCES)
+
+
 def build_all(head_dims=(16, 32, 64, 128, 256), verbose_ptxas: bool = False) -> list[str]:
     """Compile the core library and the attention library of each given head size."""
-    paths = [compile_library("janis_core", CORE_SOURCES, verbose_ptxas=verbose_ptxas)]
+    paths = [compile_library("janis_core", CORE_SOURCES, verbose_ptxas=verbose_ptxas),
+             compile_library("janis_mixers", MIXER_SOURCES, verbose_ptxas=verbose_ptxas)]
     for hd in head_dims:
         paths.append(compile_library(f"janis_attn_hd{hd}", ATTENTION_SOURCES, [f"JANIS_HEAD_DIM={hd}"],
                                      verbose_ptxas=verbose_ptxas))

@@ -246,6 +246,27 @@ gated_act8_bf16_kernel(const bf16* __restrict__ gu, bf16* __restrict__ out, size
 }
 
 // ---------------------------------------------------------------------------
+// x = act(x + bias) in place over rows of a product (bias may be absent).  ACT 0: nothing;
+// ACT 1: xIELU with two numbers per layer, a_pos = softplus(p) and a_neg = 1/2 + softplus(q), formed on the host:
+//   z > 0: a_pos z^2 + z/2;   z <= 0: a_neg (e^z - 1 - z) + z/2
+// ACT 2: the tanh form of gelu; ACT 3: silu.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+bias_act_kernel(T* __restrict__ x, const T* __restrict__ bias, size_t n, int N, int act, float a_pos, float a_neg) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float z = to_float(x[i]);
+        if (bias != nullptr) z += to_float(bias[i % N]);
+        if (act == 1) z = z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+        else if (act == 2) z = gelu_tanh(z);
+        else if (act == 3) z = z / (1.0f + expf(-z));
+        x[i] = from_float<T>(z);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // x = cap * tanh(x / cap) in place over float values (the cap on logits that a library product made)
 // ---------------------------------------------------------------------------
 __global__ void softcap_kernel(float* __restrict__ x, size_t n, float cap) {
@@ -545,6 +566,22 @@ JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows,
         return launch_kernel("gated_act", gated_act_kernel<bf16>, dim3(nb), dim3(nt), 0, stream, 1, (const bf16*)gu,
                              (bf16*)out, rows, I, group, act);
     return fail("gated_act: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_bias_act(void* x, const void* bias, int dtype, int rows, int N, int act, float a_pos, float a_neg,
+                                cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return 0;
+    if (act < 0 || act > 3) return fail("bias_act: unknown activation %d", act);
+    const size_t n = (size_t)rows * N;
+    const size_t want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want < 148 * 16 ? want : 148 * 16)), block(256);
+    if (dtype == JANIS_F32)
+        return launch_kernel("bias_act", bias_act_kernel<float>, grid, block, 0, stream, 1, (float*)x, (const float*)bias, n, N,
+                             act, a_pos, a_neg);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("bias_act", bias_act_kernel<bf16>, grid, block, 0, stream, 1, (bf16*)x, (const bf16*)bias, n, N,
+                             act, a_pos, a_neg);
+    return fail("bias_act: unknown dtype %d", dtype);
 }
 
 JANIS_EXPORT int janis_softcap(float* x, long long n, float cap, cudaStream_t stream) {

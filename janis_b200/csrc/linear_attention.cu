@@ -1,0 +1,200 @@
+// Gated linear attention: a recurrent mixer with a matrix of state per head.
+//
+//   a_t  = sigmoid(z_t)^(1/tau),   z_t = A2 (a1_t) + b        one decay per key channel (a1_t: a low-rank projection)
+//   S_t  = diag(a_t) S_{t-1} + k_t v_t^T                      S: [d, dv] float per head and sequence
+//   o_t  = S_t^T (q_t * q_scale)
+//
+// followed, in a second kernel, by an RMS norm of each head's o over dv, a gate silu(g) and the rounding to the
+// activation type.  Decays, their logarithms, the state and o are float whatever the projections are stored in.
+// The state lives in the cache (one [H, d, dv] block per slot and line): a step loads it, runs its tokens in
+// order and writes it back, so a prompt, a prompt that continues and a decode step are the same launch.
+#include "common.cuh"
+
+namespace janis {
+
+constexpr int GLA_KS = 4;          // lanes that share a column of the state (each holds every 4th key channel)
+constexpr int GLA_COLS = 32;       // value columns per CTA
+constexpr int GLA_TT = 16;         // tokens staged per round
+
+struct GlaRows {
+    int row_elems;                 // elements per row of the projected step
+    int q_off, k_off, v_off, a_off;    // where q [H, d], k [H, d], v [H, dv] and the low-rank a1 [r] start in a row
+    int H, d, dv, r;
+    float q_scale, inv_tau;
+};
+
+__device__ __forceinline__ float log_sigmoid(float z) {       // -softplus(-z), stable at both ends
+    return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+}
+
+// grid (sequences, heads, ceil(dv / GLA_COLS)); 128 threads: thread = (column, ks), ks fastest.
+template <typename T, int DPT>
+__global__ void __launch_bounds__(GLA_COLS * GLA_KS)
+gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ a2, const T* __restrict__ a2_bias,
+                const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
+                const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state,
+                float* __restrict__ o_out) {
+    extern __shared__ float smem[];
+    const int d = g.d, dv = g.dv, r = g.r, H = g.H;
+    float* q_s = smem;                       // [TT, d]
+    float* k_s = q_s + GLA_TT * d;           // [TT, d]
+    float* a_s = k_s + GLA_TT * d;           // [TT, d]
+    float* v_s = a_s + GLA_TT * d;           // [TT, GLA_COLS]
+    float* a1_s = v_s + GLA_TT * GLA_COLS;   // [TT, r]
+    const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
+    const int tid = threadIdx.x, ks = tid % GLA_KS, col = col0 + tid / GLA_KS;
+    const bool live = col < dv;
+    grid_dependents_launch();
+    const int slot = seq_slot[seq], row0 = seq_first_row[seq], n_tok = seq_end[seq] - seq_start[seq];
+    if (n_tok <= 0) return;
+    grid_dependency_wait();
+    float S[DPT];
+    float* st = slot >= 0 ? state + ((size_t)slot * H + h) * d * dv : nullptr;
+#pragma unroll
+    for (int ii = 0; ii < DPT; ++ii) {
+        const int i = ks + GLA_KS * ii;
+        S[ii] = (st != nullptr && live && i < d) ? st[(size_t)i * dv + col] : 0.f;
+    }
+    for (int t0 = 0; t0 < n_tok; t0 += GLA_TT) {
+        const int tt_n = min(GLA_TT, n_tok - t0);
+        __syncthreads();
+        for (int u = tid; u < tt_n * r; u += blockDim.x) {
+            const int tt = u / r, rr = u % r;
+            a1_s[u] = to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.a_off + rr]);
+        }
+        for (int u = tid; u < tt_n * d; u += blockDim.x) {
+            const int tt = u / d, c = u % d;
+            const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+            q_s[u] = to_float(row[g.q_off + h * d + c]) * g.q_scale;
+            k_s[u] = to_float(row[g.k_off + h * d + c]);
+        }
+        for (int u = tid; u < tt_n * GLA_COLS; u += blockDim.x) {
+            const int tt = u / GLA_COLS, c = col0 + u % GLA_COLS;
+            v_s[u] = c < dv ? to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.v_off + h * dv + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int u = tid; u < tt_n * d; u += blockDim.x) {
+            const int tt = u / d, c = u % d;
+            const T* w = a2 + (size_t)(h * d + c) * r;
+            float z = to_float(a2_bias[h * d + c]);
+            for (int rr = 0; rr < r; ++rr) z = fmaf(to_float(w[rr]), a1_s[tt * r + rr], z);
+            a_s[u] = expf(log_sigmoid(z) * g.inv_tau);
+        }
+        __syncthreads();
+        for (int tt = 0; tt < tt_n; ++tt) {
+            const float v = v_s[tt * GLA_COLS + tid / GLA_KS];
+            const float* qq = q_s + tt * d;
+            const float* kk = k_s + tt * d;
+            const float* aa = a_s + tt * d;
+            float acc = 0.f;
+#pragma unroll
+            for (int ii = 0; ii < DPT; ++ii) {
+                const int i = ks + GLA_KS * ii;
+                if (i < d) {
+                    S[ii] = fmaf(aa[i], S[ii], kk[i] * v);
+                    acc = fmaf(S[ii], qq[i], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (ks == 0 && live) o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = acc;
+        }
+    }
+    if (st != nullptr && live) {
+#pragma unroll
+        for (int ii = 0; ii < DPT; ++ii) {
+            const int i = ks + GLA_KS * ii;
+            if (i < d) st[(size_t)i * dv + col] = S[ii];
+        }
+    }
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * silu(gate[t, h, :]); a warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ rows, int row_elems, int g_off,
+                      const float* __restrict__ w, float eps, T* __restrict__ out, int n_tok, int H, int dv) {
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    if (unit >= n_tok * H) return;
+    const int t = unit / H, h = unit % H;
+    const float* src = o + ((size_t)t * H + h) * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(src[c], src[c], ss);
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+    const T* gate = rows != nullptr ? rows + (size_t)t * row_elems + g_off + h * dv : nullptr;
+    T* dst = out + ((size_t)t * H + h) * dv;
+    for (int c = lane; c < dv; c += 32) {
+        float y = src[c] * inv * w[c];
+        if (gate != nullptr) {
+            const float gv = to_float(gate[c]);
+            y *= gv / (1.0f + expf(-gv));
+        }
+        dst[c] = from_float<T>(y);
+    }
+}
+
+}  // namespace janis
+
+using namespace janis;
+
+JANIS_EXPORT void janis_mixers_set_overlap(int on) { overlap_launches() = on ? 1 : 0; }
+
+JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }
+
+template <typename T>
+static int gla_scan_launch(const void* rows, const GlaRows& g, const void* a2, const void* a2_bias, const int* seq_slot,
+                           const int* seq_first_row, const int* seq_start, const int* seq_end, float* state, float* o_out,
+                           int n_seq, cudaStream_t stream) {
+    const dim3 grid(n_seq, g.H, (g.dv + GLA_COLS - 1) / GLA_COLS), block(GLA_COLS * GLA_KS);
+    const size_t smem = ((size_t)GLA_TT * (3 * g.d + GLA_COLS + g.r)) * sizeof(float);
+#define JANIS_GLA_CASE(DPT)                                                                                            \
+    if (g.d <= GLA_KS * DPT) {                                                                                         \
+        if (smem > 48 * 1024) {                                                                                        \
+            cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return fail("gla_scan: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e)); \
+        }                                                                                                              \
+        return launch_kernel("gla_scan", gla_scan_kernel<T, DPT>, grid, block, smem, stream, 1, (const T*)rows, g,     \
+                             (const T*)a2, (const T*)a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out); \
+    }
+    JANIS_GLA_CASE(8)
+    JANIS_GLA_CASE(16)
+    JANIS_GLA_CASE(32)
+    JANIS_GLA_CASE(64)
+#undef JANIS_GLA_CASE
+    return fail("gla_scan: key size %d is above %d", g.d, GLA_KS * 64);
+}
+
+JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off, int a_off,
+                                const void* a2, const void* a2_bias, const int* seq_slot, const int* seq_first_row,
+                                const int* seq_start, const int* seq_end, float* state, float* o_out, int n_seq, int H,
+                                int d, int dv, int r, float q_scale, float tau, cudaStream_t stream) {
+    if (n_seq <= 0) return 0;
+    if (H <= 0 || d <= 0 || dv <= 0 || r <= 0) return fail("gla_scan: sizes %d heads, %d x %d, rank %d", H, d, dv, r);
+    if (!(tau > 0.f)) return fail("gla_scan: tau must be positive");
+    if (H > 65535) return fail("gla_scan: too many heads (%d)", H);
+    GlaRows g;
+    g.row_elems = row_elems; g.q_off = q_off; g.k_off = k_off; g.v_off = v_off; g.a_off = a_off;
+    g.H = H; g.d = d; g.dv = dv; g.r = r; g.q_scale = q_scale; g.inv_tau = 1.0f / tau;
+    if (dtype == JANIS_F32)
+        return gla_scan_launch<float>(rows, g, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+    if (dtype == JANIS_BF16)
+        return gla_scan_launch<bf16>(rows, g, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+    return fail("gla_scan: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_head_norm_gate(const float* o, const void* rows, int dtype, int row_elems, int g_off, const float* w,
+                                      float eps, void* out, int T, int H, int dv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const long long units = (long long)T * H;
+    const dim3 grid((unsigned)((units + 7) / 8)), block(256);
+    if (dtype == JANIS_F32)
+        return launch_kernel("head_norm_gate", head_norm_gate_kernel<float>, grid, block, 0, stream, 1, o, (const float*)rows,
+                             row_elems, g_off, w, eps, (float*)out, T, H, dv);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("head_norm_gate", head_norm_gate_kernel<bf16>, grid, block, 0, stream, 1, o, (const bf16*)rows,
+                             row_elems, g_off, w, eps, (bf16*)out, T, H, dv);
+    return fail("gla_scan: unknown dtype %d", dtype);
+}

@@ -55,6 +55,7 @@ def core():
         lib.janis_add_rmsnorm.argtypes = [P, P, I, I, c_longlong, P, F, P, F, P, I, I, I, P]
         lib.janis_gated_act.argtypes = [P, P, I, I, I, I, I, P]
         lib.janis_softcap.argtypes = [P, c_longlong, F, P]
+        lib.janis_bias_act.argtypes = [P, P, I, I, I, I, F, F, P]
         lib.janis_rope_store.argtypes = [P, I, P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, I, I, P]
         lib.janis_kv_store.argtypes = [P, I, P, P, P, P, I, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
@@ -125,6 +126,27 @@ def attention_lib(head_dim: int):
     return lib
 
 
+_mixers = None
+
+
+def mixers():
+    """The library of the mixers whose sizes are run-time numbers (compiled when a model first needs it)."""
+    global _mixers
+    if _mixers is None:
+        _need_cuda()
+        lib = build.mixers_library()
+        P, I, F = c_void_p, c_int, c_float
+        lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P]
+        lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P]
+        lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
+        lib.janis_mixers_set_overlap.argtypes = [I]
+        lib.janis_mixers_set_overlap.restype = None
+        lib.janis_mixers_set_overlap(1 if _overlap else 0)
+        _mixers = lib
+    return _mixers
+
+
 _overlap = os.environ.get("JANIS_OVERLAP", "1") != "0"
 
 
@@ -138,6 +160,8 @@ def set_overlap(on: bool) -> None:
         _core.janis_set_overlap(1 if _overlap else 0)
     for lib in _attn.values():
         lib.janis_attn_set_overlap(1 if _overlap else 0)
+    if _mixers is not None:
+        _mixers.janis_mixers_set_overlap(1 if _overlap else 0)
 
 
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
@@ -252,6 +276,19 @@ def gated_act(gu, out, act: int = ACT_GELU_TANH, group: int = GATE_GROUP):
     _check(lib, lib.janis_gated_act(_t(gu, "gu", _FLOATS, (R, 2 * I)), _t(out, "out", gu.dtype, (R, I)),
                                     _DT[gu.dtype], R, I, group, act, _stream()))
     return out
+
+
+ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN = 0, 1, 2, 3
+
+
+def bias_act(x, bias, act: int = ACT_NONE, a_pos: float = 0.0, a_neg: float = 0.0):
+    """x = act(x + bias) in place over [R, N] (bias [N] of x's dtype, or None).  ACT_XIELU takes the two numbers
+    a_pos and a_neg: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (e^z - 1 - z) + z/2."""
+    R, N = x.shape
+    lib = core()
+    _check(lib, lib.janis_bias_act(_t(x, "x", _FLOATS, (R, N)), _t(bias, "bias", x.dtype, (N,)) if bias is not None else None,
+                                   _DT[x.dtype], R, N, int(act), float(a_pos), float(a_neg), _stream()))
+    return x
 
 
 def rope_store(qkv, tok_pos, tok_seq, seq_slot, seq_end, inv_freq, rot: int, nq: int, nkv: int, hd: int,
@@ -455,10 +492,10 @@ class WaitWatch:
 
 
 def linear_bf16(x, w, out):
-    """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 16 rows,
-    the library product (cuBLAS) above."""
+    """out[M, N] = x w^T in bfloat16 with float accumulation: the skinny kernel up to 16 rows (inner sizes that
+    are multiples of 8), the library product (cuBLAS) otherwise."""
     M = x.shape[0]
-    if M <= GEMV_FAST_ROWS:
+    if M <= GEMV_FAST_ROWS and x.shape[1] % 8 == 0:
         return gemv_bf16(x, w, out)
     _t(x, "x", torch.bfloat16)
     _t(w, "w", torch.bfloat16)
@@ -697,6 +734,109 @@ def attn_decode(qkv, kpool, vpool, page_table, seq_slot, seq_len, scratch, out, 
                                       scratch.data_ptr(), scratch.numel(), out.data_ptr(), n_seq, nq, nkv,
                                       qkv.shape[1], float(scale), float(cap), int(window), int(ring_len),
                                       int(chunk), int(max_chunks), _stream()), kernels=1 if direct else 2)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# mixers with run-time sizes: attention with mixed heads, gated linear attention
+# ---------------------------------------------------------------------------
+
+def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, H: int, G: int, d: int, dv: int,
+                     kpool=None, vpool=None, page_table=None, store: bool = True):
+    """Rotary encoding of the first `rot` features of the queries and keys of a step (pairs i, i + rot/2), rotation
+    of the values over all dv features by inv_v (None: values stay as projected), and the write of keys and values
+    into the paged cache line.  rows [T, H d + G d + G dv] holds q, then k, then v; with store=False the rows hold q
+    alone.  kpool [pages, G, PAGE, d], vpool [pages, G, PAGE, dv]."""
+    T, width = rows.shape
+    _t(rows, "rows", _FLOATS, (T, None))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("qkv_rotate_store: position tables shorter than the step")
+    _t(inv_qk, "inv_qk", torch.float32, (rot // 2,))
+    if inv_v is not None:
+        _t(inv_v, "inv_v", torch.float32, (dv // 2,))
+    stride = 0
+    if store:
+        n_pages = kpool.shape[0]
+        _t(kpool, "kpool", rows.dtype, (n_pages, G, PAGE, d))
+        _t(vpool, "vpool", rows.dtype, (n_pages, G, PAGE, dv))
+        _t(page_table, "page_table", torch.int32, (None, None))
+        _t(seq_slot, "seq_slot", torch.int32)
+        stride = page_table.shape[1]
+    lib = mixers()
+    _check(lib, lib.janis_qkv_rotate_store(
+        rows.data_ptr(), _DT[rows.dtype], width, _t(tok_pos, "tok_pos", torch.int32), _t(tok_seq, "tok_seq", torch.int32),
+        seq_slot.data_ptr() if store else None, inv_qk.data_ptr() if rot else None, rot,
+        inv_v.data_ptr() if inv_v is not None else None, T, H, G, d, dv, 1 if store else 0,
+        kpool.data_ptr() if store else None, vpool.data_ptr() if store else None,
+        page_table.data_ptr() if store else None, stride, _stream()))
+    return rows
+
+
+def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
+                   d: int, dv: int, scale: float, block: int = 0, sink: bool = False):
+    """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
+    own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
+    alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
+    with sink, 1 is added to the softmax's denominator; with inv_v each head's output is turned back by the query's
+    position (the cached values were rotated by theirs).  q_rows [T, >= H d], out [T, H dv]."""
+    T = q_rows.shape[0]
+    _t(q_rows, "q_rows", _FLOATS, (T, None))
+    n_pages = kpool.shape[0]
+    _t(kpool, "kpool", q_rows.dtype, (n_pages, G, PAGE, d))
+    _t(vpool, "vpool", q_rows.dtype, (n_pages, G, PAGE, dv))
+    _t(page_table, "page_table", torch.int32, (None, None))
+    _t(out, "out", q_rows.dtype, (T, H * dv))
+    if tok_pos.numel() < T or tok_seq.numel() < T:
+        raise KernelError("talk_attention: position tables shorter than the step")
+    lib = mixers()
+    _check(lib, lib.janis_talk_attention(
+        q_rows.data_ptr(), _DT[q_rows.dtype], q_rows.shape[1], _t(tok_pos, "tok_pos", torch.int32),
+        _t(tok_seq, "tok_seq", torch.int32), _t(seq_slot, "seq_slot", torch.int32), kpool.data_ptr(), vpool.data_ptr(),
+        page_table.data_ptr(), page_table.shape[1],
+        _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None,
+        _t(inv_v, "inv_v", torch.float32, (dv // 2,)) if inv_v is not None else None, out.data_ptr(), T, H, G, d, dv,
+        float(scale), int(block), 1 if sink else 0, _stream()))
+    return out
+
+
+def gla_scan(rows, q_off: int, k_off: int, v_off: int, a_off: int, a2, a2_bias, seq_slot, seq_first_row, seq_start,
+             seq_end, state, o_out, n_seq: int, H: int, d: int, dv: int, r: int, q_scale: float, tau: float):
+    """The recurrence of gated linear attention over the tokens each sequence brings to the step, in order:
+    a = sigmoid(a2 a1 + a2_bias)^(1/tau) per key channel, S = diag(a) S + k v^T, o = S^T (q q_scale).
+    rows [T, width] holds the projections (q [H, d] at q_off, k at k_off, v [H, dv] at v_off, a1 [r] at a_off);
+    state float32 [slots, H, d, dv] is read and written back for sequences whose slot is >= 0; o_out float32
+    [T, H dv]."""
+    T, width = rows.shape
+    _t(rows, "rows", _FLOATS, (T, None))
+    _t(a2, "a2", rows.dtype, (H * d, r))
+    _t(a2_bias, "a2_bias", rows.dtype, (H * d,))
+    _t(state, "state", torch.float32, (None, H, d, dv))
+    _t(o_out, "o_out", torch.float32, (T, H * dv))
+    for name, tab in (("seq_slot", seq_slot), ("seq_first_row", seq_first_row), ("seq_start", seq_start), ("seq_end", seq_end)):
+        _t(tab, name, torch.int32)
+        if tab.numel() < n_seq:
+            raise KernelError(f"gla_scan: {name} shorter than the step's sequences")
+    lib = mixers()
+    _check(lib, lib.janis_gla_scan(rows.data_ptr(), _DT[rows.dtype], width, q_off, k_off, v_off, a_off, a2.data_ptr(),
+                                   a2_bias.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
+                                   seq_end.data_ptr(), state.data_ptr(), o_out.data_ptr(), n_seq, H, d, dv, r,
+                                   float(q_scale), float(tau), _stream()))
+    return o_out
+
+
+def head_norm_gate(o, rows, g_off: int, weight, eps: float, out, H: int, dv: int):
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per head of dv features; the gate
+    is read from rows [T, width] at g_off (rows None: no gate).  o float32 [T, H dv], weight float32 [dv]."""
+    T = o.shape[0]
+    _t(o, "o", torch.float32, (T, H * dv))
+    _t(weight, "weight", torch.float32, (dv,))
+    _t(out, "out", _FLOATS, (T, H * dv))
+    if rows is not None:
+        _t(rows, "rows", out.dtype, (T, None))
+    lib = mixers()
+    _check(lib, lib.janis_head_norm_gate(o.data_ptr(), rows.data_ptr() if rows is not None else None, _DT[out.dtype],
+                                         rows.shape[1] if rows is not None else 0, g_off, weight.data_ptr(), float(eps),
+                                         out.data_ptr(), T, H, dv, _stream()))
     return out
 
 

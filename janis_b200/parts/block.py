@@ -3,7 +3,7 @@
 `SandwichBlock` is Gemma2's (`gemma/gemma.go:162-167`): a norm before and a
 norm after each sublayer, the second applied to the sublayer's output before it
 is added:  r = Mixer(N_in(x)); h = x + N_post_mixer(r); r = FF(N_pre_ff(h));
-out = h + N_post_ff(r).
+out = h + N_post_ff(r).  Without a feed-forward (`feed_forward=None`) a layer is the first line alone.
 
 `PreNormBlock` is the usual arrangement without the norms after the sublayers
 (`qwen/block.go:58-61`): h = x + Mixer(N_in(x)); out = h + FF(N_pre_ff(h)).
@@ -20,13 +20,17 @@ from .norm import plain_residual_add
 
 
 class SandwichBlock(Block):
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, input_norm: Norm, post_mixer_norm: Norm,
-                 pre_ff_norm: Norm, post_ff_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, input_norm: Norm, post_mixer_norm: Norm,
+                 pre_ff_norm: Norm | None = None, post_ff_norm: Norm | None = None):
+        if feed_forward is not None and (pre_ff_norm is None or post_ff_norm is None):
+            raise ValueError("a block with a feed-forward needs the norms before and after it")
         self.mixer, self.feed_forward = mixer, feed_forward
         self.first_norm = input_norm
         self.post_mixer_norm, self.pre_ff_norm, self.post_ff_norm = post_mixer_norm, pre_ff_norm, post_ff_norm
 
     def sub_parts(self):
+        if self.feed_forward is None:
+            return [self.first_norm, self.mixer, self.post_mixer_norm]
         return [self.first_norm, self.mixer, self.post_mixer_norm, self.pre_ff_norm, self.feed_forward,
                 self.post_ff_norm]
 
@@ -35,6 +39,9 @@ class SandwichBlock(Block):
         dt = ctx.rt.dtype
         y = y_in if y_in is not None else self.first_norm.forward(h, ctx, ctx.ws.buf("block.y", (T, H), dt))
         r = self.mixer.forward(y, ctx, line)
+        if self.feed_forward is None:
+            return h, self.post_mixer_norm.residual_add(h, r, ctx, next_norm, ctx.ws.buf("block.y", (T, H), dt)
+                                                        if next_norm is not None else None)
         y = self.post_mixer_norm.residual_add(h, r, ctx, self.pre_ff_norm, ctx.ws.buf("block.y", (T, H), dt))
         r = self.feed_forward.forward(y, ctx)
         y_next = self.post_ff_norm.residual_add(h, r, ctx, next_norm,

@@ -14,10 +14,12 @@ from .base import Part, Runtime, StepContext
 
 
 class Embedding(Part):
-    def __init__(self, vocab: int, hidden: int, table_name: str, scale: float = 1.0, init_std: float = 0.02):
+    def __init__(self, vocab: int, hidden: int, table_name: str, scale: float = 1.0, init_std: float = 0.02,
+                 round_scale: bool = True):
         self.vocab, self.hidden = vocab, hidden
         self.table_name = table_name
         self.scale = float(scale)
+        self.round_scale = bool(round_scale)    # False: the constant multiplies as a float32 whatever the activations are
         self.init_std = init_std
         self.table = None
         self.scale_used = self.scale
@@ -29,7 +31,7 @@ class Embedding(Part):
         self.table = store.get(self.table_name, rt.dtype).contiguous()
         # the reference casts the scalar to the activation dtype before the multiply (`mlxc/mlxc.go:587-601`):
         # in bfloat16 sqrt(2304) = 48 stays exact, sqrt(3584) = 59.87 becomes 59.75
-        self.scale_used = float(torch.tensor(self.scale, dtype=torch.float32).to(rt.dtype))
+        self.scale_used = float(torch.tensor(self.scale, dtype=torch.float32).to(rt.dtype if self.round_scale else torch.float32))
 
     def forward(self, tokens, ctx: StepContext, out):
         return ctx.rt.ops.embed(tokens, self.table, self.scale_used, out)

@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: down(act(gate(x)) * up(x)), no biases.
+"""Dense feed-forwards: the gated one, down(act(gate(x)) * up(x)) without biases, and the plain one,
+down(act(up(x) + b_up)) + b_down (`DenseMLP`, at the end of the file).
 
 Gemma2's is GeGLU with the tanh form of gelu (`gemma/gemma.go:121-123`;
 0.5 v (1 + tanh(0.7978845608028654 (v + 0.044715 v^3))), `cpu/cpu.go:417-423`);
@@ -12,6 +13,8 @@ applied to float accumulators before anything is written.  Above 16 rows the
 product comes from the library and a separate kernel applies the activation.
 """
 from __future__ import annotations
+
+import math
 
 import torch
 
@@ -74,3 +77,67 @@ class GatedMLP(FeedForward):
             ops.gated_act(gu, a, self.act, self.GROUP)
         out = ws.buf("ffn.out", (T, self.hidden), rt.dtype)
         return rt.linear(a, self.w_down, out)
+
+
+def _softplus(v: float) -> float:
+    return max(v, 0.0) + math.log1p(math.exp(-abs(v)))
+
+
+class DenseMLP(FeedForward):
+    """down(act(up(x) + b_up)) + b_down, the biases optional.
+
+    act: "gelu_tanh", "silu", or "xielu", a piecewise activation with two learnt numbers (p, q) per layer, stored
+    as a tensor of two values under names["act"]:
+        z > 0:   softplus(p) z^2 + z/2
+        z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z/2
+    The two factors are formed once, at load, in double precision."""
+
+    def __init__(self, hidden: int, intermediate: int, names: dict[str, str], act: str = "xielu",
+                 init_std: float = 0.02):
+        if act not in ("xielu", "gelu_tanh", "silu"):
+            raise ValueError(f"unknown activation {act!r} (known: gelu_tanh, silu, xielu)")
+        for k in ("up", "down"):
+            if k not in names:
+                raise ValueError(f"feed-forward needs the checkpoint name of its {k!r} projection")
+        if act == "xielu" and "act" not in names:
+            raise ValueError("the xielu activation needs the checkpoint name of its two numbers ('act')")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.act = act
+        self.names = dict(names)
+        self.init_std = init_std
+        self.w_up = self.w_down = self.b_up = self.b_down = None
+        self.a_pos = self.a_neg = 0.0
+
+    def tensor_specs(self):
+        H, I, s, n = self.hidden, self.intermediate, self.init_std, self.names
+        specs = {n["up"]: TensorSpec((I, H), init_std=s), n["down"]: TensorSpec((H, I), init_std=s)}
+        if "up_bias" in n:
+            specs[n["up_bias"]] = TensorSpec((I,), init_std=s)
+        if "down_bias" in n:
+            specs[n["down_bias"]] = TensorSpec((H,), init_std=s)
+        if self.act == "xielu":
+            specs[n["act"]] = TensorSpec((2,), init_std=0.5)
+        return specs
+
+    def load(self, store, rt: Runtime):
+        n = self.names
+        self.w_up = store.get(n["up"], rt.dtype).contiguous()
+        self.w_down = store.get(n["down"], rt.dtype).contiguous()
+        self.b_up = store.get(n["up_bias"], rt.dtype).contiguous() if "up_bias" in n else None
+        self.b_down = store.get(n["down_bias"], rt.dtype).contiguous() if "down_bias" in n else None
+        if self.act == "xielu":
+            p, q = (float(v) for v in store.get(n["act"]).to(torch.float64).cpu().tolist())
+            self.a_pos, self.a_neg = _softplus(p), 0.5 + _softplus(q)
+
+    def forward(self, x, ctx: StepContext):
+        rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
+        T = ctx.n_tok
+        a = ws.buf("ffn.act", (T, self.intermediate), rt.dtype)
+        rt.linear(x, self.w_up, a)
+        kind = {"xielu": ops.ACT_XIELU, "gelu_tanh": ops.ACT_GELU, "silu": ops.ACT_SILU_PLAIN}[self.act]
+        ops.bias_act(a, self.b_up, kind, self.a_pos, self.a_neg)
+        out = ws.buf("ffn.out", (T, self.hidden), rt.dtype)
+        rt.linear(a, self.w_down, out)
+        if self.b_down is not None:
+            ops.bias_act(out, self.b_down, ops.ACT_NONE)
+        return out

@@ -14,16 +14,17 @@ from .base import Norm, Runtime, StepContext
 
 
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float, weight_name: str, offset: float = 0.0, init_std: float = 0.1):
+    def __init__(self, width: int, eps: float, weight_name: str, offset: float = 0.0, init_std: float = 0.1,
+                 init_mean: float = 0.0):
         self.width = width
         self.eps = float(eps)
         self.offset = float(offset)
         self.weight_name = weight_name
-        self.init_std = init_std
+        self.init_std, self.init_mean = init_std, init_mean      # how random weights are drawn
         self.weight = None          # float32: offset + w
 
     def tensor_specs(self):
-        return {self.weight_name: TensorSpec((self.width,), init_std=self.init_std)}
+        return {self.weight_name: TensorSpec((self.width,), init_std=self.init_std, init_mean=self.init_mean)}
 
     def load(self, store, rt: Runtime):
         self.weight = (store.get(self.weight_name).to(torch.float32) + self.offset).contiguous()

@@ -41,12 +41,17 @@ def _register_builtin() -> None:
     from .attention import SoftmaxAttention
     from .block import PreNormBlock, SandwichBlock
     from .embedding import Embedding, LMHead
-    from .feedforward import GatedMLP
+    from .feedforward import DenseMLP, GatedMLP
+    from .linear_attention import GatedLinearAttention
+    from .talking_attention import TalkingHeadsAttention
     from .norm import RMSNorm
     from .position import NoPosition, RotaryEncoding
 
     register("mixer", "softmax_attention", SoftmaxAttention)
+    register("mixer", "talking_heads_attention", TalkingHeadsAttention)   # heads mixed before the softmax, sink, block mask
+    register("mixer", "gated_linear_attention", GatedLinearAttention)     # a matrix of state per head, decays per key channel
     register("feed_forward", "gated_mlp", GatedMLP)
+    register("feed_forward", "dense_mlp", DenseMLP)                       # up, activation, down, with biases
     register("norm", "rms_norm", RMSNorm)
     register("position", "rotary", RotaryEncoding)
     register("position", "none", NoPosition)

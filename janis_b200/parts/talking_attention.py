@@ -1,0 +1,104 @@
+"""Softmax attention whose heads are mixed before the softmax, with values of a size of their own.
+
+With H query heads over G key/value heads (query head h uses key/value head h // (H/G)), keys of d features
+and values of dv:
+
+    raw_g[i, j] = (q_g[i] . k[j]) * scale                     positions encoded on q and k by `position`
+    s_h[i, j]   = sum_g M[h, g] raw_g[i, j]                   M: a stored H x H matrix (names["talk"]; absent: none)
+    p_h[i, j]   = exp(s_h[i, j]) / (sink + sum_j' exp(s_h[i, j']))
+    o_h[i]      = sum_j p_h[i, j] v[j]
+
+over the keys j <= i that lie in the query's block of `block` positions (block 0: all of them; blocks are counted
+from the sequence's first position).  `sink` adds 1 to the denominator: a key of score 0 that has no value.  With a
+`value_position` the values are rotated by their own position before they are cached (over all dv features) and
+each head's output is turned back by the query's position, so that o depends on relative positions only.
+
+Keys and values live in a paged cache line with separate head sizes.  A step writes its keys and values first
+and then attends over the line alone, so a prompt, a prompt that continues, a decode step and a layer that reads
+the line of another layer (`own_kv=False`: queries only, no key/value tensors of its own) are one code path.
+Scores, the mixing, the softmax and the sums are float32 whatever the activations are.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.cache import KVNeed
+from ..weights.loader import TensorSpec
+from .base import Mixer, Runtime, StepContext
+from .position import RotaryEncoding
+
+
+class TalkingHeadsAttention(Mixer):
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, scale: float,
+                 position: RotaryEncoding, names: dict[str, str], value_position: RotaryEncoding | None = None,
+                 block: int = 0, sink: bool = False, own_kv: bool = True, init_std: float = 0.02):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} query heads do not divide over {n_kv_heads} key/value heads")
+        need = ("q", "k", "v", "o") if own_kv else ("q", "o")
+        for k in need:
+            if k not in names:
+                raise ValueError(f"attention needs the checkpoint name of its {k!r} projection")
+        if value_position is not None and (value_position.rot != value_dim or value_dim % 2):
+            raise ValueError("rotated values turn all of their features, in pairs")
+        self.hidden, self.n_heads, self.n_kv_heads = hidden, n_heads, n_kv_heads
+        self.key_dim, self.value_dim = key_dim, value_dim
+        self.scale = float(scale)
+        self.block = int(block or 0)
+        self.sink = bool(sink)
+        self.own_kv = bool(own_kv)
+        self.position, self.value_position = position, value_position
+        self.names = dict(names)
+        self.init_std = init_std
+        self.w_qkv = self.w_o = self.talk = None
+
+    def tensor_specs(self):
+        H, G, d, dv, W, s, n = self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim, self.hidden, self.init_std, self.names
+        specs = {n["q"]: TensorSpec((H * d, W), init_std=s), n["o"]: TensorSpec((W, H * dv), init_std=s)}
+        if self.own_kv:
+            specs[n["k"]] = TensorSpec((G * d, W), init_std=s)
+            specs[n["v"]] = TensorSpec((G * dv, W), init_std=s)
+        if "talk" in n:
+            specs[n["talk"]] = TensorSpec((H, H), init_std=H ** -0.5)
+        return specs
+
+    def sub_parts(self):
+        return [p for p in (self.position, self.value_position) if p is not None]
+
+    def cache_needs(self):
+        return {"kv": KVNeed(self.n_kv_heads, self.key_dim, None, self.value_dim)}
+
+    def prompt_flops(self, n_tokens: int) -> float:
+        B = self.block or n_tokens
+        full, rest = divmod(n_tokens, B)
+        seen = full * (B * (B + 1) // 2) + rest * (rest + 1) // 2         # (query, key) pairs
+        return seen * 2.0 * self.n_heads * (self.key_dim + self.value_dim + ("talk" in self.names) * self.n_heads)
+
+    def load(self, store, rt: Runtime):
+        n = self.names
+        if self.own_kv:
+            q, k, v = (store.get(n[x], rt.dtype) for x in ("q", "k", "v"))
+            self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
+            del q, k, v
+            store.drop(n["q"], n["k"], n["v"])
+        else:
+            self.w_qkv = store.get(n["q"], rt.dtype).contiguous()
+        self.w_o = store.get(n["o"], rt.dtype).contiguous()
+        self.talk = store.get(n["talk"]).to(torch.float32).contiguous() if "talk" in n else None
+
+    def forward(self, x, ctx: StepContext, line):
+        rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
+        kv = line["kv"]
+        if kv.write != self.own_kv:
+            raise ValueError("the schedule lets a layer with keys and values of its own only read a line, or the reverse")
+        T, H, G, d, dv = ctx.n_tok, self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
+        width = H * d + (G * (d + dv) if self.own_kv else 0)
+        rows = ws.buf("tattn.rows", (T, width), rt.dtype)
+        rt.linear(x, self.w_qkv, rows)
+        inv_v = self.value_position.inv_freq if self.value_position is not None else None
+        ops.qkv_rotate_store(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, self.position.inv_freq, self.position.rot,
+                             inv_v, H, G, d, dv, kv.k if self.own_kv else None, kv.v if self.own_kv else None,
+                             kv.table if self.own_kv else None, store=self.own_kv)
+        att = ws.buf("tattn.ctx", (T, H * dv), rt.dtype)
+        ops.talk_attention(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, self.talk, inv_v, att,
+                           H, G, d, dv, self.scale, self.block, self.sink)
+        return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

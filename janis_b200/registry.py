@@ -45,7 +45,7 @@ def architectures() -> tuple[str, ...]:
 
 def resolve(raw: Mapping[str, Any], where: str = "config.json") -> Architecture:
     """The architecture that a parsed config.json names."""
-    names = raw.get("architectures") or []
+    names = raw.get("architectures") or raw.get("architecture") or []      # a list, or one name under either key
     if isinstance(names, str):
         names = [names]
     for n in names:

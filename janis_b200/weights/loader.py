@@ -33,11 +33,12 @@ class WeightsError(ValueError):
 
 @dataclass(frozen=True)
 class TensorSpec:
-    """One expected tensor: its shape, whether it is an integer table, and how
-    the random-weights mode draws it (normal with `init_std`)."""
-    shape: tuple[int, ...]
+    """One expected tensor: its shape (None for an extent that the stored tensor decides, a low rank for
+    instance), whether it is an integer table, and how the random-weights mode draws it (normal with `init_std`)."""
+    shape: tuple[int | None, ...]
     integer: bool = False
     init_std: float = 0.02
+    init_mean: float = 0.0
 
 
 _FLOATS = {"F64", "F32", "F16", "BF16"}
@@ -55,7 +56,7 @@ def check_tensors(expected: Mapping[str, TensorSpec], files: ModelFiles,
     wrong = []
     for n in sorted(want & have):
         info, spec = files.info(n), expected[n]
-        if tuple(info.shape) != tuple(spec.shape):
+        if len(info.shape) != len(spec.shape) or any(w is not None and w != h for w, h in zip(spec.shape, info.shape)):
             wrong.append(f"{n}: expected shape {list(spec.shape)}, found {list(info.shape)}")
         elif spec.integer and info.dtype not in _INTS:
             wrong.append(f"{n}: expected an integer table, found dtype {info.dtype}")
@@ -148,6 +149,9 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, device="cpu",
     """The tensor that (seed, name) names, the same bits on every device: a counter-based generator keyed by the
     seed, the name and the element's index, so the values depend neither on which other tensors are drawn, nor
     on their order, nor on where they are drawn."""
+    if any(d is None for d in spec.shape):
+        raise WeightsError(f"{name}: an extent of its shape {list(spec.shape)} is left to the stored tensor; random weights "
+                           "need it in the configuration")
     key = _tensor_seed(seed, name) >> 3           # room for the counters' low bits within 63 bits
     n = 1
     for d in spec.shape:
@@ -160,10 +164,11 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, device="cpu",
             out[a:a + m] = (_hash64(i * 4 + (1 + key)) & 0x7FFF).to(torch.int32)
         return out.view(spec.shape)
     out = torch.empty(n, device=device, dtype=dtype)
-    std = float(spec.init_std)
+    std, mean = float(spec.init_std), float(spec.init_mean)
     for a in range(0, n, _CHUNK):
         m = min(_CHUNK, n - a)
-        out[a:a + m] = (_bell(key, a, m, device) * std).to(dtype)
+        x = _bell(key, a, m, device) * std
+        out[a:a + m] = (x + mean if mean else x).to(dtype)
     return out.view(spec.shape)
 
 

@@ -290,3 +290,116 @@ def mask_tokens(logits, ids):
         if 0 <= tok < logits.shape[1]:
             logits[:, tok] = float("-inf")
     return logits
+
+
+# ---------------------------------------------------------------------------
+# mixers with run-time sizes
+# ---------------------------------------------------------------------------
+
+ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN = 0, 1, 2, 3
+
+
+def bias_act(x, bias, act=ACT_NONE, a_pos=0.0, a_neg=0.0):
+    z = x.double()
+    if bias is not None:
+        z = z + bias.double()
+    if act == ACT_XIELU:
+        z = torch.where(z > 0, a_pos * z * z + 0.5 * z, a_neg * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z)
+    elif act == ACT_GELU:
+        z = _act(z, ACT_GELU_TANH)
+    elif act == ACT_SILU_PLAIN:
+        z = _act(z, ACT_SILU)
+    x.copy_(z.to(x.dtype))
+    return x
+
+
+def _turn(x, pos, inv, sign=1.0):
+    """x [..., n] rotated by sign * pos * inv over pairs (i, i + len(inv)); angles float32 as the kernels form them."""
+    h = inv.numel()
+    if h == 0:
+        return x
+    theta = (torch.as_tensor(float(pos), dtype=torch.float32) * inv.float()).double()
+    c, s = torch.cos(theta), sign * torch.sin(theta)
+    a, b = x[..., :h].double(), x[..., h:2 * h].double()
+    return torch.cat([a * c - b * s, a * s + b * c, x[..., 2 * h:].double()], dim=-1)
+
+
+def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G, d, dv, kpool=None, vpool=None,
+                     page_table=None, store=True):
+    T = rows.shape[0]
+    for t in range(T):
+        pos = int(tok_pos[t])
+        n = H + G if store else H
+        qk = rows[t, :n * d].view(n, d)
+        qk.copy_(_turn(qk, pos, inv_qk).to(rows.dtype))
+        if not store:
+            continue
+        v = rows[t, n * d:n * d + G * dv].view(G, dv)
+        if inv_v is not None:
+            v.copy_(_turn(v, pos, inv_v).to(rows.dtype))
+        slot = int(seq_slot[int(tok_seq[t])])
+        if slot < 0:
+            continue
+        page = int(page_table[slot, pos // PAGE])
+        kpool[page, :, pos % PAGE] = qk[H:]
+        vpool[page, :, pos % PAGE] = v
+    return rows
+
+
+def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
+                   block=0, sink=False):
+    T = q_rows.shape[0]
+    rep = H // G
+    for t in range(T):
+        pos, slot = int(tok_pos[t]), int(seq_slot[int(tok_seq[t])])
+        if slot < 0:
+            out[t] = 0
+            continue
+        first = (pos // block) * block if block > 0 else 0
+        js = list(range(first, pos + 1))
+        pages = [int(page_table[slot, j // PAGE]) for j in js]
+        k = torch.stack([kpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, d]
+        v = torch.stack([vpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, dv]
+        q = q_rows[t, :H * d].view(H, d).double()
+        raw = torch.einsum("hd,nhd->hn", q, k.repeat_interleave(rep, dim=1)) * scale
+        s = talk.double() @ raw if talk is not None else raw
+        m = torch.clamp(s.max(dim=1, keepdim=True).values, min=0.0)
+        e = torch.exp(s - m)
+        p = e / ((torch.exp(-m) if sink else 0.0) + e.sum(dim=1, keepdim=True))
+        o = torch.einsum("hn,nhv->hv", p, v.repeat_interleave(rep, dim=1))
+        if inv_v is not None:
+            o = _turn(o, pos, inv_v, sign=-1.0)
+        out[t] = o.reshape(-1).to(out.dtype)
+    return out
+
+
+def gla_scan(rows, q_off, k_off, v_off, a_off, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out,
+             n_seq, H, d, dv, r, q_scale, tau):
+    for s in range(n_seq):
+        slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
+        if n <= 0:
+            continue
+        S = state[slot].double().clone() if slot >= 0 else torch.zeros(H, d, dv, dtype=torch.float64)
+        for t in range(row0, row0 + n):
+            row = rows[t].double()
+            q = row[q_off:q_off + H * d].view(H, d) * q_scale
+            k = row[k_off:k_off + H * d].view(H, d)
+            v = row[v_off:v_off + H * dv].view(H, dv)
+            z = a2.double() @ row[a_off:a_off + r] + a2_bias.double()
+            a = torch.exp(torch.nn.functional.logsigmoid(z) / tau).view(H, d)
+            S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
+            o_out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).float()
+        if slot >= 0:
+            state[slot] = S.float()
+    return o_out
+
+
+def head_norm_gate(o, rows, g_off, weight, eps, out, H, dv):
+    T = o.shape[0]
+    x = o.double().view(T, H, dv)
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+    if rows is not None:
+        g = rows[:, g_off:g_off + H * dv].double().view(T, H, dv)
+        y = y * g * torch.sigmoid(g)
+    out.copy_(y.reshape(T, H * dv).to(out.dtype))
+    return out
