@@ -1,0 +1,444 @@
+"""Sigalorn: each mechanism against its plain statement, and the engine against the plain model.
+
+The configurations are small and differ from each other in every size and option: grouped and ungrouped heads,
+values wider and narrower than keys, rotary widths below the key size, block sizes that are no multiple of a cache
+page (and a block of one position), layers with and without a feed-forward, a layer that reads another's keys,
+low ranks, several tau.  Weights are seeded random ones with the query/key projections scaled up, so that the
+attention weights are far from uniform and a key that is wrongly seen or missed changes the logits.
+
+Engine cases run on the GPU (`-m gpu`, float32 and bfloat16) and, as a check of the host side alone, on the CPU
+over the plain kernel statements (float32, shorter requests).
+"""
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+from tests.conftest import random_tokens
+from tests.helpers import assert_logits, make_engine, run_in_pieces, run_requests
+
+GPU = pytest.mark.gpu
+CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloat16", marks=GPU),
+         pytest.param("refs", "float32")]
+
+
+def _att(heads, kv, dim, vdim, rot, block, scale, base=10000.0, kv_from=None):
+    m = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "scale": scale, "rot": {"base": base, "dims": rot},
+         "mask": {"size": block}}
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def _gla(heads, dim, vdim, tau, rank):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau, "rank": rank}
+
+
+def _layer(kind, mixer, ff):
+    return {"type": kind, "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if ff else None}
+
+
+SIG_A = {"architecture": "Sigalorn", "vocab": 200, "width": 64, "embedding": {"scale": 1.7}, "norm": {"eps": 1e-6},
+         "logit_softcap": 10.0, "layers": [
+             _layer("gla", _gla(2, 16, 24, 8.0, 8), 96),
+             _layer("attention", _att(4, 2, 32, 16, 16, 24, 0.2), 72),
+             _layer("attention", _att(4, 2, 32, 16, 16, 40, 0.15, kv_from=1), None),
+             _layer("gla", _gla(3, 8, 8, 1.0, 4), 96)]}
+
+SIG_B = {"architecture": "Sigalorn", "vocab": 333, "width": 96, "embedding": {"scale": 0.3}, "norm": {"eps": 1e-5},
+         "logit_softcap": 25.0, "layers": [
+             _layer("attention", _att(3, 3, 16, 32, 16, 70, 0.25, base=1000.0), 128),
+             _layer("gla", _gla(1, 40, 48, 32.0, 24), None),
+             _layer("attention", _att(6, 1, 24, 8, 8, 1, 0.3), 160),
+             _layer("attention", _att(2, 1, 48, 40, 0, 128, 0.1), 64)]}
+
+# one layer of each kind at sizes a tensor-core kernel would take: blocks of two whole pages
+SIG_C = {"architecture": "Sigalorn", "vocab": 512, "width": 128, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+         "logit_softcap": 30.0, "layers": [
+             _layer("attention", _att(8, 2, 64, 64, 64, 128, 0.125, base=500000.0), 256),
+             _layer("gla", _gla(2, 64, 128, 16.0, 16), 256),
+             _layer("attention", _att(8, 2, 64, 64, 64, 100, 0.125, base=500000.0, kv_from=0), 256)]}
+
+SIG = {"A": SIG_A, "B": SIG_B, "C": SIG_C}
+
+
+def write_sigalorn(model_dir: str, raw: dict, seed: int) -> None:
+    """A folder of seeded random weights: query and key projections scaled up, the head-mixing matrix near the
+    identity, decay biases spread around 1."""
+    from janis_b200 import build_model
+    from janis_b200.weights.loader import random_tensors, write_model_folder
+    _, cfg, model = build_model(raw)
+    tensors = random_tensors(model.tensor_specs(), seed, "cpu")
+    for name, t in list(tensors.items()):
+        if name.endswith(".mix.q") or name.endswith(".mix.k"):
+            tensors[name] = (t.float() * 6.0).to(torch.bfloat16)
+        elif name.endswith(".mix.talk"):
+            tensors[name] = (torch.eye(t.shape[0]) + 0.6 * t.float()).to(torch.bfloat16)
+        elif name.endswith(".mix.a2.b"):
+            tensors[name] = (t.float() * 2.0 + 1.0).to(torch.bfloat16)
+        elif name.endswith(".mix.v") or name.endswith(".mix.o") or name.endswith(".mlp.up") or name.endswith(".mlp.down"):
+            tensors[name] = (t.float() * 4.0).to(torch.bfloat16)
+    write_model_folder(model_dir, cfg.to_dict(), tensors, {"seed": str(seed)})
+
+
+@pytest.fixture(scope="module")
+def sig_dirs(tmp_path_factory):
+    out = {}
+    for i, (key, raw) in enumerate(SIG.items()):
+        d = tmp_path_factory.mktemp(f"sigalorn_{key}")
+        write_sigalorn(str(d), raw, 100 + i)
+        out[key] = str(d)
+    return out
+
+
+@pytest.fixture(scope="module")
+def plain(sig_dirs):
+    from tests.plain import sigalorn_plain as P
+    loaded = {k: P.load_folder(d) for k, d in sig_dirs.items()}
+    memo = {}
+
+    def logits(key, tokens):
+        k = (key, tuple(tokens))
+        if k not in memo:
+            cfg, w = loaded[key]
+            memo[k] = P.forward(cfg, w, list(tokens))
+        return memo[k]
+
+    return logits
+
+
+@pytest.fixture(scope="module")
+def engines(sig_dirs):
+    made = {}
+
+    def get(key, dtype, on, **kw):
+        k = (key, dtype, on, tuple(sorted(kw.items())))
+        if k not in made:
+            made[k] = make_engine(sig_dirs[key], dtype, on, **kw)
+        return made[k]
+
+    yield get
+    for e in made.values():
+        e.close()
+
+
+def keys_for(on):
+    return ["A", "B", "C"] if on == "cuda" else ["A", "B"]
+
+
+# ---------------------------------------------------------------------------
+# configuration and registry
+# ---------------------------------------------------------------------------
+
+def test_configuration_reads_back_and_guards():
+    from janis_b200 import ConfigError, SigalornConfig, build_model, resolve
+    cfg = SigalornConfig.from_dict(SIG_A)
+    assert SigalornConfig.from_dict(cfg.to_dict()) == cfg
+    assert resolve(SIG_A).name == "Sigalorn"
+    assert cfg.layers[2].mixer.kv_from == 1 and cfg.layers[2].mlp is None and cfg.layers[1].mixer.block == 24
+    _, _, model = build_model(SIG_A)
+    assert [(c.layer, c.cache_line, c.write) for c in model.schedule] == [(0, 0, True), (1, 1, True), (2, 1, False), (3, 2, True)]
+    assert "l2.mix.k" not in model.tensor_specs() and "l2.norm2" not in model.tensor_specs()
+    bad = {**SIG_A, "layers": [SIG_A["layers"][2]]}
+    with pytest.raises(ConfigError):
+        SigalornConfig.from_dict(bad)                      # kv_from names no earlier layer
+    odd = {**SIG_A, "layers": [_layer("attention", _att(4, 3, 32, 16, 16, 24, 0.2), 72)]}
+    with pytest.raises(ConfigError):
+        SigalornConfig.from_dict(odd)                      # heads do not divide
+    with pytest.raises(ConfigError):
+        SigalornConfig.from_dict({**SIG_A, "layers": [{"type": "conv", "mixer": {}, "mlp": None}]})
+
+
+def test_a_low_rank_is_read_from_the_stored_tensor(tmp_path):
+    """Without `rank` in the configuration the stored tensor decides."""
+    import copy
+    import json
+    import os
+    write_sigalorn(str(tmp_path), SIG_A, 5)
+    raw = copy.deepcopy(SIG_A)
+    for layer in raw["layers"]:
+        layer["mixer"].pop("rank", None)
+    with open(os.path.join(tmp_path, "config.json"), "w") as f:
+        json.dump(raw, f)
+    eng = make_engine(str(tmp_path), "float32", "refs", max_tokens=128)
+    assert [b.mixer.rank for b in eng.model.blocks if hasattr(b.mixer, "rank")] == [8, 4]
+    eng.close()
+
+
+# ---------------------------------------------------------------------------
+# each mechanism alone: the kernels against tests/kernel_refs.py (GPU), and the plain oracle's functions against
+# hand-made cases (CPU)
+# ---------------------------------------------------------------------------
+
+def test_plain_xielu_and_sink_by_hand():
+    from tests.plain import sigalorn_plain as P
+    z = torch.tensor([-2.0, 0.0, 3.0], dtype=torch.float64)
+    p, q = torch.tensor(0.5, dtype=torch.float64), torch.tensor(-1.0, dtype=torch.float64)
+    sp, sq = math.log1p(math.exp(0.5)), math.log1p(math.exp(-1.0))
+    want = [(0.5 + sq) * (math.exp(-2.0) - 1 + 2.0) - 1.0, 0.0, sp * 9.0 + 1.5]
+    assert torch.allclose(P.xielu(z, p, q), torch.tensor(want, dtype=torch.float64), atol=1e-12)
+    # one token, one head: the sink takes 1 / (1 + e^s) of the weight
+    m = {"heads": 1, "kv_heads": 1, "dim": 2, "vdim": 2, "scale": 1.0, "rot": {"base": 10.0, "dims": 0}, "mask": {"size": 4}}
+    eye = torch.eye(2, dtype=torch.float64)
+    w = {"q": eye, "k": eye, "v": eye, "o": eye, "talk": torch.ones(1, 1, dtype=torch.float64)}
+    y = torch.tensor([[1.0, 2.0]], dtype=torch.float64)
+    k, v = P.attention_keys_values(y, w, "", m)
+    out = P.attention_mixer(y, w, "", m, k, v)
+    assert torch.allclose(out, y * (math.exp(5.0) / (1.0 + math.exp(5.0))), atol=1e-12)
+
+
+def _paged(n_seq, lens, G, d, dv, dtype, seed, spare=3):
+    """Random keys and values of n_seq sequences scattered over a page pool in a shuffled order."""
+    from janis_b200.kernels.ops import PAGE
+    g = torch.Generator().manual_seed(seed)
+    per = [(n + PAGE - 1) // PAGE for n in lens]
+    n_pages = sum(per) + spare
+    order = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.zeros(n_seq + 2, max(per), dtype=torch.int32)
+    slots = torch.randperm(n_seq + 2, generator=g)[:n_seq].to(torch.int32)
+    at = 0
+    for s in range(n_seq):
+        for j in range(per[s]):
+            table[int(slots[s]), j] = order[at]
+            at += 1
+    k = torch.randn(n_pages, G, PAGE, d, generator=g).to(dtype)
+    v = torch.randn(n_pages, G, PAGE, dv, generator=g).to(dtype)
+    return k, v, table, slots
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,dv,block,sink,talk,turn", [
+    (4, 2, 32, 16, 24, True, True, True), (6, 6, 64, 32, 200, True, True, True), (3, 1, 24, 40, 1, True, False, False),
+    (8, 2, 64, 64, 128, False, True, True), (2, 2, 16, 8, 0, False, False, True), (5, 5, 8, 6, 7, True, True, False)])
+def test_attention_kernel_against_its_statement(dtype, H, G, d, dv, block, sink, talk, turn):
+    """Queries at chosen positions (a block's first and last place, a page's border, far into the sequence) over
+    scattered pages; one far key made to stand out for each query."""
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    lens = [1, 70, 129, 300]
+    kp, vp, table, slots = _paged(len(lens), lens, G, d, dv, dtype, 3)
+    pos, seq = [], []
+    for s, n in enumerate(lens):
+        for p in sorted({0, n - 1, n // 2, min(n - 1, 63), min(n - 1, 64), min(n - 1, max(block, 1) - 1),
+                         min(n - 1, max(block, 1)), min(n - 1, 2 * max(block, 1))}):
+            pos.append(p)
+            seq.append(s)
+    T = len(pos)
+    g = torch.Generator().manual_seed(9)
+    q = torch.randn(T, H * d + 5, generator=g).to(dtype)
+    # the first key each query sees gets a large score under head 0
+    for t in range(T):
+        first = (pos[t] // block) * block if block else 0
+        page = int(table[int(slots[seq[t]]), first // ops.PAGE])
+        kp[page, 0, first % ops.PAGE] = (q[t, :d].float() * (3.0 / max(q[t, :d].float().norm().item(), 1e-3))).to(dtype)
+    M = (torch.eye(H) + 0.3 * torch.randn(H, H, generator=g)).float() if talk else None
+    inv_v = torch.tensor([10000.0 ** (-2.0 * m / dv) for m in range(dv // 2)], dtype=torch.float32) if turn else None
+    tok_pos, tok_seq = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
+    want = torch.zeros(T, H * dv, dtype=dtype)
+    R.talk_attention(q, tok_pos, tok_seq, slots, kp, vp, table, M, inv_v, want, H, G, d, dv, 0.4, block, sink)
+    dev = lambda x: x.cuda() if x is not None else None
+    got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
+    ops.talk_attention(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), dev(M), dev(inv_v), got,
+                       H, G, d, dv, 0.4, block, sink)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    err = (got.cpu().double() - want.double()).abs().max().item()
+    assert err <= tol * max(1.0, want.double().abs().max().item()), err
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,G,d,dv,rot,turn", [(4, 2, 32, 16, 16, True), (3, 3, 16, 32, 16, False), (2, 1, 48, 40, 0, True)])
+def test_rotation_and_cache_write_against_their_statement(dtype, H, G, d, dv, rot, turn):
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    lens = [5, 130]
+    _, _, table, slots = _paged(2, lens, G, d, dv, dtype, 4)
+    slots[0] = -1 if False else slots[0]
+    n_pages = int(table.max()) + 1
+    pos = [0, 1, 2, 3, 4] + [0, 63, 64, 65, 127, 128, 129]
+    seq = [0] * 5 + [1] * 7
+    T = len(pos)
+    g = torch.Generator().manual_seed(2)
+    rows = torch.randn(T, H * d + G * d + G * dv, generator=g).to(dtype)
+    inv_qk = torch.tensor([500.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float32)
+    inv_v = torch.tensor([500.0 ** (-2.0 * m / dv) for m in range(dv // 2)], dtype=torch.float32) if turn else None
+    tok_pos, tok_seq = torch.tensor(pos, dtype=torch.int32), torch.tensor(seq, dtype=torch.int32)
+    for store in (True, False):
+        width = rows.shape[1] if store else H * d
+        r_cpu = rows[:, :width].clone().contiguous()
+        k_cpu, v_cpu = torch.zeros(n_pages, G, ops.PAGE, d, dtype=dtype), torch.zeros(n_pages, G, ops.PAGE, dv, dtype=dtype)
+        R.qkv_rotate_store(r_cpu, tok_pos, tok_seq, slots, inv_qk, rot, inv_v, H, G, d, dv, k_cpu, v_cpu, table, store)
+        r_dev = rows[:, :width].clone().contiguous().cuda()
+        k_dev, v_dev = torch.zeros_like(k_cpu).cuda(), torch.zeros_like(v_cpu).cuda()
+        ops.qkv_rotate_store(r_dev, tok_pos.cuda(), tok_seq.cuda(), slots.cuda(), inv_qk.cuda(), rot,
+                             inv_v.cuda() if turn else None, H, G, d, dv, k_dev if store else None,
+                             v_dev if store else None, table.cuda() if store else None, store)
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        for a, b in ((r_dev, r_cpu), (k_dev, k_cpu), (v_dev, v_cpu)):
+            assert (a.cpu().double() - b.double()).abs().max().item() <= tol * 6.0
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,d,dv,r,tau", [(2, 16, 24, 8, 8.0), (1, 40, 48, 24, 32.0), (3, 8, 8, 4, 1.0), (2, 128, 72, 16, 16.0),
+                                          (1, 200, 32, 2, 4.0)])
+def test_recurrence_kernel_against_its_statement(dtype, H, d, dv, r, tau):
+    """Sequences of 1, 17 and 40 tokens (one without a slot), the second step continuing from the state the
+    first one left; then the head norm and gate."""
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(6)
+    lens = [1, 17, 40]
+    T = sum(lens)
+    width = 2 * H * d + 2 * H * dv + r
+    a2 = (0.3 * torch.randn(H * d, r, generator=g)).to(dtype)
+    b2 = (1.0 + torch.randn(H * d, generator=g)).to(dtype)
+    state_cpu = torch.zeros(4, H, d, dv)
+    state_dev = state_cpu.clone().cuda()
+    slots = torch.tensor([2, -1, 0], dtype=torch.int32)
+    first = torch.tensor([0, 1, 18], dtype=torch.int32)
+    start = torch.zeros(3, dtype=torch.int32)
+    offs = (0, H * d, 2 * H * d, 2 * H * d + 2 * H * dv)
+    for step in range(2):
+        rows = torch.randn(T, width, generator=g).to(dtype)
+        end = start + torch.tensor(lens, dtype=torch.int32)
+        want = torch.zeros(T, H * dv)
+        R.gla_scan(rows, *offs, a2, b2, slots, first, start, end, state_cpu, want, 3, H, d, dv, r, d ** -0.5, tau)
+        got = torch.full((T, H * dv), float("nan"), device="cuda")
+        ops.gla_scan(rows.cuda(), *offs, a2.cuda(), b2.cuda(), slots.cuda(), first.cuda(), start.cuda(), end.cuda(),
+                     state_dev, got, 3, H, d, dv, r, d ** -0.5, tau)
+        scale = max(1.0, want.abs().max().item())
+        assert (got.cpu() - want).abs().max().item() <= 2e-5 * scale
+        assert (state_dev.cpu() - state_cpu).abs().max().item() <= 2e-5 * max(1.0, state_cpu.abs().max().item())
+        assert state_dev[1].abs().max().item() == 0 and state_dev[3].abs().max().item() == 0      # untouched slots
+        w = (1.0 + 0.2 * torch.randn(dv, generator=g)).float()
+        y_want = torch.zeros(T, H * dv, dtype=dtype)
+        R.head_norm_gate(want, rows, 2 * H * d + H * dv, w, 1e-5, y_want, H, dv)
+        y_got = torch.zeros(T, H * dv, dtype=dtype, device="cuda")
+        ops.head_norm_gate(got, rows.cuda(), 2 * H * d + H * dv, w.cuda(), 1e-5, y_got, H, dv)
+        tol = 2e-5 if dtype == torch.float32 else 2e-2
+        assert (y_got.cpu().double() - y_want.double()).abs().max().item() <= tol * max(1.0, y_want.double().abs().max().item())
+        start = end
+
+
+@GPU
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_bias_and_activation_kernel_against_its_statement(dtype):
+    from janis_b200.kernels import ops
+    from tests import kernel_refs as R
+    g = torch.Generator().manual_seed(1)
+    x = (3.0 * torch.randn(37, 72, generator=g)).to(dtype)
+    b = torch.randn(72, generator=g).to(dtype)
+    for act, bias in ((ops.ACT_XIELU, b), (ops.ACT_NONE, b), (ops.ACT_XIELU, None), (ops.ACT_GELU, b), (ops.ACT_SILU_PLAIN, None)):
+        want = R.bias_act(x.clone(), bias, act, 0.9, 0.7)
+        got = ops.bias_act(x.clone().cuda(), bias.cuda() if bias is not None else None, act, 0.9, 0.7)
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert (got.cpu().double() - want.double()).abs().max().item() <= tol * max(1.0, want.double().abs().max().item())
+
+
+# ---------------------------------------------------------------------------
+# the engine against the plain model
+# ---------------------------------------------------------------------------
+
+def _lengths(on):
+    return ((1, 1), (2, 2), (23, 3), (25, 4), (71, 5), (150, 6), (300, 7)) if on == "cuda" else ((1, 1), (2, 2), (27, 3), (75, 4))
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_whole_prompts_and_first_tokens(on, dtype, engines, plain):
+    for key in keys_for(on):
+        eng = engines(key, dtype, on, max_tokens=1024)
+        for n, seed in _lengths(on):
+            req = random_tokens(SIG[key]["vocab"], n, seed)
+            got = run_requests(eng, [req], [n])[0]
+            assert_logits(got, plain(key, req), dtype, f"{key} whole n={n}")
+        assert eng.cache.live_slots() == []
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_prompt_then_token_by_token(on, dtype, engines, plain):
+    """Decoding crosses block edges (24, 40, 70, 100, 128 positions) and page borders; one request decodes from its
+    first token on."""
+    cases = ((150, 20, 8), (140, 120, 9), (70, 1, 10)) if on == "cuda" else ((60, 20, 8), (30, 1, 10))
+    for key in keys_for(on):
+        eng = engines(key, dtype, on, max_tokens=1024)
+        for n, prompt, seed in cases:
+            req = random_tokens(SIG[key]["vocab"], n, seed)
+            got = run_requests(eng, [req], [prompt])[0]
+            assert_logits(got, plain(key, req), dtype, f"{key} prompt {prompt} of {n}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_unequal_batches_with_slots_used_again(on, dtype, engines, plain):
+    lens = [5, 31, 17, 1, 49, 23, 90, 70, 3, 131] if on == "cuda" else [5, 31, 1, 40, 26, 3]
+    prompts = [3, 11, 9, 1, 25, 20, 80, 38, 1, 100] if on == "cuda" else [3, 11, 1, 25, 24, 1]
+    for key in keys_for(on):
+        reqs = [random_tokens(SIG[key]["vocab"], n, 40 + i) for i, n in enumerate(lens)]
+        eng = engines(key, dtype, on, max_tokens=6 * 64, max_batch=4)
+        got = run_requests(eng, reqs, prompts, max_live=3)
+        for i, (g, r) in enumerate(zip(got, reqs)):
+            assert_logits(g, plain(key, r), dtype, f"{key} request {i} in batches of 3")
+        eng.cache.audit()
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+@pytest.mark.parametrize("chunk", [2, 7, 64])
+def test_a_prompt_that_comes_in_pieces(on, dtype, chunk, engines, plain):
+    if on == "refs" and chunk == 2:
+        pytest.skip("slow on the CPU; covered by 7")
+    for key in keys_for(on):
+        eng = engines(key, dtype, on, max_tokens=1024)
+        lens = (45, 130) if on == "cuda" else (30, 19)
+        reqs = [random_tokens(SIG[key]["vocab"], n, 60 + n) for n in lens]
+        got = run_in_pieces(eng, reqs, chunk)
+        for g, r in zip(got, reqs):
+            assert_logits(g, plain(key, r), dtype, f"{key} in pieces of {chunk}")
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_graphs_agree_with_plain_launches(dtype, sig_dirs, plain):
+    """260 tokens decoded one by one from a prompt of 3, with recorded steps and with plain launches: the same
+    logits, and the plain model's."""
+    req = random_tokens(SIG["A"]["vocab"], 263, 77)
+    outs = []
+    for graphs in (True, False):
+        eng = make_engine(sig_dirs["A"], dtype, "cuda", max_tokens=512, use_graphs=graphs)
+        outs.append(run_requests(eng, [req], [3])[0])
+        eng.close()
+    assert_logits(outs[0], plain("A", req), dtype, "long decoding")
+    assert torch.equal(outs[0], outs[1])
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_company_changes_nothing(dtype, engines, plain):
+    """A request's logits are the same bits alone and beside others."""
+    key = "B"
+    eng = engines(key, dtype, "cuda", max_tokens=1024)
+    reqs = [random_tokens(SIG[key]["vocab"], n, 90 + n) for n in (80, 9, 33)]
+    alone = run_requests(eng, [reqs[0]], [60])[0]
+    beside = run_requests(eng, reqs, [60, 5, 20])[0]
+    assert torch.equal(alone, beside)
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_greedy_generation_through_the_entry_point(on, dtype, engines, plain):
+    """`Engine.generate` (scheduler, sampler, cache) against greedy decoding with the plain model."""
+    key = "A"
+    eng = engines(key, dtype, on, max_tokens=1024)
+    prompts = [random_tokens(SIG[key]["vocab"], n, 70 + n) for n in ((9, 30, 2) if on == "cuda" else (9, 3))]
+    new = 12 if on == "cuda" else 5
+    replies = eng.generate(prompts, temp=0.0, max_tokens=new, stop=[])
+    for p, reply in zip(prompts, replies):
+        assert len(reply) == new
+        seq = list(p)
+        for tok in reply:
+            ref = plain(key, seq)[-1]
+            top2 = torch.topk(ref, 2).values
+            if dtype == "float32" or (top2[0] - top2[1]).item() > 0.1:
+                assert tok == int(ref.argmax()), f"token {len(seq) - len(p)} of the reply"
+            seq.append(tok)
