@@ -140,7 +140,7 @@ def prefill_flops(model, n_tokens: int) -> float:
     layer's mixer says it computes beyond its products (attention: scores and weighted sums)."""
     flops = 0.0
     for name, spec in model.tensor_specs().items():
-        if len(spec.shape) == 2 and "embed_tokens" not in name:
+        if len(spec.shape) == 2 and name != getattr(model.embedding, "table_name", None):
             flops += 2.0 * n_tokens * spec.shape[0] * spec.shape[1]
     for call in model.schedule:
         flops += float(model.blocks[call.layer].mixer.prompt_flops(n_tokens))
@@ -433,6 +433,155 @@ def other_sizes(pk: dict, warmup: int = 8) -> dict:
     return out
 
 
+# ---------------------------------------------------------------------------
+# two designs side by side at equal layer sizes (`--compare sigalorn`)
+# ---------------------------------------------------------------------------
+
+class KernelTimer:
+    """CUDA events around chosen functions of the kernels module while a step runs launch by launch: the device
+    time of each, summed per name.  (Events between kernels keep a kernel's CTAs from arriving while its
+    predecessor still runs, so a step timed this way is slower than the same step untimed; the shares are what
+    is read.)"""
+
+    def __init__(self, ops, names):
+        self.ops, self.names = ops, [n for n in names if hasattr(ops, n)]
+        self.events: dict[str, list] = {n: [] for n in self.names}
+        self._orig = {}
+
+    def __enter__(self):
+        for n in self.names:
+            orig = getattr(self.ops, n)
+            self._orig[n] = orig
+
+            def timed(*a, _orig=orig, _n=n, **k):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                r = _orig(*a, **k)
+                e1.record()
+                self.events[_n].append((e0, e1))
+                return r
+
+            setattr(self.ops, n, timed)
+        return self
+
+    def __exit__(self, *exc):
+        for n, orig in self._orig.items():
+            setattr(self.ops, n, orig)
+        return False
+
+    def totals_us(self) -> dict:
+        torch.cuda.synchronize()
+        return {n: round(sum(a.elapsed_time(b) for a, b in ev) * 1e3, 1) for n, ev in self.events.items() if ev}
+
+
+def sigalorn_like(gemma: dict, layers: int) -> dict:
+    """A Sigalorn configuration with the layer sizes of a Gemma2 one: the same width, heads, head size (for keys
+    and values), feed-forward width and vocabulary; attention blocks as long as Gemma2's window; layers alternate
+    attention and gated linear attention (its key channels half the head size, at most 256), and the second
+    attention layer of every four reads the keys and values of the first."""
+    hd = int(gemma["head_dim"])
+    att = {"heads": gemma["num_attention_heads"], "kv_heads": gemma["num_key_value_heads"], "dim": hd, "vdim": hd,
+           "scale": hd ** -0.5, "rot": {"base": 10000.0, "dims": hd}, "mask": {"size": int(gemma.get("sliding_window", 4096))}}
+    gla = {"heads": gemma["num_attention_heads"], "dim": min(256, hd // 2), "vdim": hd, "tau": 16.0, "rank": 64}
+    mlp = {"kind": "dense", "ff": gemma["intermediate_size"]}
+    out = []
+    for i in range(layers):
+        if i % 2:
+            out.append({"type": "gla", "mixer": dict(gla), "mlp": dict(mlp)})
+        elif i % 4 == 2:
+            out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2), "mlp": dict(mlp)})
+        else:
+            out.append({"type": "attention", "mixer": dict(att), "mlp": dict(mlp)})
+    return {"architecture": "Sigalorn", "vocab": gemma["vocab_size"], "width": gemma["hidden_size"],
+            "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": out}
+
+
+_TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_norm_gate", "bias_act"),
+          "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act")}
+
+
+def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: int, context: int, steps: int,
+                    warmup: int) -> dict:
+    import janis_b200
+    from .engine.step import StepEntry
+    eng = janis_b200.from_config(raw, seed=0, dtype="bfloat16", max_tokens=batch * max(context, prefill_tokens) + 64,
+                                 max_batch=batch, max_context=max(context, prefill_tokens))
+    ops, model = eng.rt.ops, eng.model
+    out = {"layers": len(model.blocks)}
+    pre = measure_prefill(eng, prefill_tokens, repeats=3, warmup=2)
+    out["prefill_tok_s"] = round(pre["tok_s"], 1)
+    out["prefill_ms"] = round(pre["ms"], 3)
+    out["prefill_frac_of_bf16_peak"] = round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)
+    dec = measure_decode(eng, [context - steps - warmup] * batch, steps, warmup)
+    out["decode_tok_s"] = round(dec["tok_s"], 1)
+    out["decode_ms_per_step"] = round(dec["ms_per_step"], 4)
+    out["decode_frac_of_copy_bandwidth"] = _frac(dec, pk)
+    # the kernels of one prompt step and of one decode step, launch by launch
+    kernels = {}
+    slot = eng.alloc_slot()
+    with KernelTimer(ops, _TIMED[kind]) as kt:
+        eng.stepper.step([StepEntry(slot, _tokens(model.vocab, prefill_tokens, 1), (prefill_tokens - 1,))])
+    kernels["prefill_us"] = kt.totals_us()
+    eng.free_slot(slot)
+    slots = fill(eng, [context - 1] * batch)
+    graphs, eng.stepper.use_graphs = eng.stepper.use_graphs, False
+    entries = [StepEntry(s, (1,), (0,)) for s in slots]
+    eng.stepper.step(entries)
+    with KernelTimer(ops, _TIMED[kind]) as kt:
+        eng.stepper.step(entries)
+    kernels["decode_us"] = kt.totals_us()
+    eng.stepper.use_graphs = graphs
+    for s in slots:
+        eng.free_slot(s)
+    # what those kernels must compute or read, from the mixers' own account
+    from .cache.cache import KVNeed, StateNeed
+    att_flops = gla_flops = 0.0
+    kv_bytes = state_bytes = 0
+    for call in model.schedule:
+        mixer = model.blocks[call.layer].mixer
+        for need in mixer.cache_needs().values():
+            if isinstance(need, KVNeed):
+                att_flops += mixer.prompt_flops(prefill_tokens)
+                seen = min(context, need.window) if need.window else context
+                seen = min(seen, (context - 1) % mixer.block + 1) if getattr(mixer, "block", 0) else seen
+                kv_bytes += batch * seen * need.n_kv_heads * (need.head_dim + need.value_dim) * 2
+            elif isinstance(need, StateNeed):
+                gla_flops += mixer.prompt_flops(prefill_tokens)
+                state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
+    att_name = "talk_attention" if kind == "sigalorn" else "attn_prefill"
+    dec_name = "talk_attention" if kind == "sigalorn" else "attn_decode"
+    roof = {}
+    if kernels["prefill_us"].get(att_name):
+        roof["attention_prefill_frac_of_bf16_peak"] = round(att_flops / (kernels["prefill_us"][att_name] * 1e-6) / (pk["bf16_tflops"] * 1e12), 5)
+    if kernels["decode_us"].get(dec_name):
+        roof["attention_decode_frac_of_copy_bandwidth"] = round(kv_bytes / (kernels["decode_us"][dec_name] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    if kernels["prefill_us"].get("gla_scan"):
+        roof["recurrence_prefill_tflops_fp32"] = round(gla_flops / (kernels["prefill_us"]["gla_scan"] * 1e-6) / 1e12, 3)
+    if kernels["decode_us"].get("gla_scan"):
+        roof["recurrence_decode_frac_of_copy_bandwidth"] = round(state_bytes / (kernels["decode_us"]["gla_scan"] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    out["kernels"] = kernels
+    out["kernel_rooflines"] = roof
+    eng.close()
+    return out
+
+
+def compare(sizes=("gemma2-2b", "gemma2-9b", "gemma2-27b"), layers: int = 4, prefill_tokens: int = 2048, batch: int = 8,
+            context: int = 4096, steps: int = 64, warmup: int = 4) -> dict:
+    """Sigalorn beside Gemma2 at the layer sizes of the Gemma2 configurations, `layers` layers each, random
+    weights: prompt tokens a second, decode tokens a second, and the device time of each design's own kernels in
+    one prompt step and one decode step with what fraction of the roofline that is."""
+    pk, pk_kind = peaks()
+    rec = {"compare": "sigalorn beside gemma2", "dtype": "bf16", "data": "synthetic", "peaks": pk_kind,
+           "prefill_tokens": prefill_tokens, "batch": batch, "context": context, "steps": steps, "sizes": {}}
+    for name in sizes:
+        gemma = dict(load_config(name), num_hidden_layers=layers)
+        gemma.pop("layer_types", None)
+        rec["sizes"][name] = {
+            "gemma2": _measure_design(gemma, "gemma2", pk, prefill_tokens, batch, context, steps, warmup),
+            "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup)}
+    return rec
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="janis bench")
     ap.add_argument("--gpus", type=int, default=1)
@@ -454,6 +603,9 @@ def main(argv=None) -> int:
                     "instead of sequences that all reach --context")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
+    ap.add_argument("--compare", choices=["sigalorn"], default="",
+                    help="instead of the benchmark: Sigalorn beside Gemma2 at equal layer sizes (prompt and decode "
+                    "throughput, and each design's own kernels against their rooflines); --config picks one size")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go module (no Go toolchain here, "
@@ -462,6 +614,12 @@ def main(argv=None) -> int:
     if a.gpus != 1:
         print(f"janis_b200 is a one-GPU library: --gpus {a.gpus} is not supported")
         return 2
+    if a.compare:
+        sizes = ("gemma2-2b", "gemma2-9b", "gemma2-27b") if a.config == "gemma2-2b" and "--config" not in (argv or sys.argv) \
+            else ((a.config if a.config.startswith("gemma2-") else "gemma2-" + a.config),)
+        print(json.dumps(compare(sizes, a.layers or 4, a.prefill, int(str(a.batch).split(",")[0]), min(a.context, 4096),
+                                 min(a.steps, 64), max(3, min(a.warmup, 8)))))
+        return 0
     try:
         batches = [int(b) for b in str(a.batch).split(",") if b.strip()]
     except ValueError:

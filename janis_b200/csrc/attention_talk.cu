@@ -230,6 +230,295 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
     }
 }
 
+// ---------------------------------------------------------------------------
+// The tensor-core kernel (bfloat16, d a multiple of 16, dv a multiple of 8, up to 32 heads).
+//
+// A CTA of 8 warps owns up to QR (16 or 8) consecutive rows of the packed step, all heads together, since every
+// head's weights need every head's scores.  Rows of one sequence form a run; a run's keys (from the first row's
+// block start to the last row's position) come in tiles of BN keys.  Per tile, three phases with the scores
+// passing through shared memory as floats:
+//   1. raw_g = Q_g K^T * scale for every head (mma.sync m16n8k16, operands by ldmatrix; items (head, 8 keys)
+//      dealt to the warps);
+//   2. a thread per (row, key) mixes the heads' scores in float registers and applies the mask; a warp per (head,
+//      row) then does the online softmax (maximum, exponentials, sum) and leaves P as bfloat16;
+//   3. O_h = O_h * corr + P_h V (mma.sync; V through ldmatrix.trans; items (head, 8 value columns) dealt to the
+//      warps), the accumulators living in shared memory as floats so that all sizes are run-time numbers.
+// Keys and values of a tile take turns in one buffer.  With QR = 8 the upper half of every 16-row operand repeats
+// the lower one and is dropped: big heads fit shared memory that way.  A decode step runs one row a CTA.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src));
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+struct TalkMmaShape {
+    int H, G, d, dv, block, sink;
+    int qr;             // rows of the operands kept (16 or 8)
+    int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
+    int bn;             // keys per tile (16, 32, 64)
+    float scale;
+};
+
+struct TalkMmaLayout {
+    size_t q, kv, raw, p, o, m, l, corr, talk, meta, total;
+    int qs, kvs, rs, ps, os;       // row strides in elements
+};
+
+__host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, int dv, int qr, int bn) {
+    TalkMmaLayout L;
+    L.qs = d + 8; L.kvs = (d > dv ? d : dv) + 8; L.rs = bn + 4; L.ps = bn + 8; L.os = dv + 4;
+    size_t at = 0;
+    L.q = at;    at += (size_t)H * qr * L.qs * 2;
+    L.kv = at;   at += (size_t)G * bn * L.kvs * 2;
+    L.p = at;    at += (size_t)H * qr * L.ps * 2;
+    at = (at + 15) & ~(size_t)15;
+    L.raw = at;  at += (size_t)H * qr * L.rs * 4;
+    L.o = at;    at += (size_t)H * qr * L.os * 4;
+    L.m = at;    at += (size_t)H * qr * 4;
+    L.l = at;    at += (size_t)H * qr * 4;
+    L.corr = at; at += (size_t)H * qr * 4;
+    L.talk = at; at += (size_t)H * H * 4;
+    L.meta = at; at += 3 * 16 * 4;
+    L.total = at;
+    return L;
+}
+
+template <int HMAX>
+__global__ void __launch_bounds__(256)
+talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, const int* __restrict__ tok_pos,
+                          const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                          const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
+                          const int* __restrict__ page_table, int table_stride, const float* __restrict__ talk,
+                          const float* __restrict__ inv_v, bf16* __restrict__ out, int n_tok, TalkMmaShape sh) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int H = sh.H, G = sh.G, d = sh.d, dv = sh.dv, QR = sh.qr, BN = sh.bn, rep = H / G;
+    const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, QR, BN);
+    bf16* q_s = reinterpret_cast<bf16*>(smem_raw + L.q);
+    bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + L.kv);
+    bf16* p_s = reinterpret_cast<bf16*>(smem_raw + L.p);
+    float* raw_s = reinterpret_cast<float*>(smem_raw + L.raw);
+    float* o_s = reinterpret_cast<float*>(smem_raw + L.o);
+    float* m_s = reinterpret_cast<float*>(smem_raw + L.m);
+    float* l_s = reinterpret_cast<float*>(smem_raw + L.l);
+    float* corr_s = reinterpret_cast<float*>(smem_raw + L.corr);
+    float* talk_s = reinterpret_cast<float*>(smem_raw + L.talk);
+    int* pos_s = reinterpret_cast<int*>(smem_raw + L.meta);
+    int* seq_s = pos_s + 16;
+    int* slot_s = pos_s + 32;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int r0 = blockIdx.x * sh.rows, n_rows = min(sh.rows, n_tok - r0);
+    grid_dependents_launch();
+    if (tid < 16) {
+        const bool in = tid < n_rows;
+        const int sq = in ? tok_seq[r0 + tid] : -1;
+        pos_s[tid] = in ? tok_pos[r0 + tid] : 0;
+        seq_s[tid] = sq;
+        slot_s[tid] = in ? seq_slot[sq] : -1;
+    }
+    if (talk != nullptr)
+        for (int u = tid; u < H * H; u += 256) talk_s[u] = talk[u];
+    for (int u = tid; u < H * QR * L.os; u += 256) o_s[u] = 0.f;
+    for (int u = tid; u < H * QR; u += 256) {
+        m_s[u] = sh.sink ? 0.f : -CUDART_INF_F;
+        l_s[u] = sh.sink ? 1.f : 0.f;
+    }
+    grid_dependency_wait();
+    {   // queries: rows of the step, 16 bytes at a time; rows beyond the step's end are zero
+        const int cpr = d / 8;
+        for (int u = tid; u < H * QR * cpr; u += 256) {
+            const int c8 = u % cpr, r = (u / cpr) % QR, h = u / (cpr * QR);
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (r < n_rows) v = *reinterpret_cast<const uint4*>(q_rows + (size_t)(r0 + r) * q_row_elems + (size_t)h * d + c8 * 8);
+            *reinterpret_cast<uint4*>(q_s + ((size_t)h * QR + r) * L.qs + c8 * 8) = v;
+        }
+    }
+    __syncthreads();
+    int a = 0;
+    while (a < n_rows) {
+        int b = a + 1;
+        while (b < n_rows && seq_s[b] == seq_s[a]) ++b;
+        const int slot = slot_s[a];
+        if (slot >= 0) {
+            const int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
+            const int* table = page_table + (size_t)slot * table_stride;
+            for (int j0 = first; j0 <= last; j0 += BN) {
+                // ---- keys of the tile
+                {
+                    const int cpr = d / 8;
+                    for (int u = tid; u < G * BN * cpr; u += 256) {
+                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), j = j0 + jj;
+                        bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
+                        if (j <= last)
+                            cp_async16(smem_u32(dst), kpool + (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * d + c8 * 8);
+                        else
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                    }
+                    cp_async_wait_all();
+                }
+                __syncthreads();
+                // ---- 1: raw scores of every head
+                {
+                    const int nts = BN / 8;
+                    for (int item = warp; item < H * nts; item += 8) {
+                        const int g = item / nts, nt = item % nts, kvh = g / rep;
+                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                        const uint32_t a_base = smem_u32(q_s + ((size_t)g * QR + ((lane & 15) & (QR - 1))) * L.qs + (lane >> 4) * 8);
+                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + nt * 8 + (lane & 7)) * L.kvs + ((lane >> 3) & 1) * 8);
+                        for (int kk = 0; kk < d / 16; ++kk) {
+                            uint32_t af[4], bfr[2];
+                            ldsm_x4(af, a_base + kk * 32);
+                            ldsm_x2(bfr, b_base + kk * 32);
+                            mma_bf16(acc, af, bfr);
+                        }
+                        const int r = lane >> 2, c = nt * 8 + (lane & 3) * 2;
+                        float* dst = raw_s + ((size_t)g * QR + r) * L.rs + c;
+                        dst[0] = acc[0] * sh.scale;
+                        dst[1] = acc[1] * sh.scale;
+                        if (QR == 16) {
+                            dst[8 * L.rs] = acc[2] * sh.scale;
+                            dst[8 * L.rs + 1] = acc[3] * sh.scale;
+                        }
+                    }
+                }
+                __syncthreads();
+                // ---- 2a: the heads' scores mixed, the mask
+                for (int pair = tid; pair < QR * BN; pair += 256) {
+                    const int r = pair / BN, c = pair % BN, j = j0 + c;
+                    bool seen = r >= a && r < b && j <= pos_s[r];
+                    if (seen && sh.block > 0) seen = j >= (pos_s[r] / sh.block) * sh.block;
+                    float* at = raw_s + (size_t)r * L.rs + c;
+                    const size_t hs = (size_t)QR * L.rs;
+                    if (!seen) {
+                        for (int h = 0; h < H; ++h) at[h * hs] = -CUDART_INF_F;
+                    } else if (talk != nullptr) {
+                        float raw[HMAX];
+#pragma unroll
+                        for (int g = 0; g < HMAX; ++g) raw[g] = g < H ? at[g * hs] : 0.f;
+                        for (int h = 0; h < H; ++h) {
+                            const float* tr = talk_s + h * H;
+                            float s = 0.f;
+#pragma unroll
+                            for (int g = 0; g < HMAX; ++g)
+                                if (g < H) s = fmaf(tr[g], raw[g], s);
+                            at[h * hs] = s;
+                        }
+                    }
+                }
+                __syncthreads();
+                // ---- 2b: online softmax of every (head, row); P as bfloat16
+                for (int u = warp; u < H * QR; u += 8) {
+                    const float* src = raw_s + (size_t)u * L.rs;
+                    const float s0 = lane < BN ? src[lane] : -CUDART_INF_F;
+                    const float s1 = lane + 32 < BN ? src[lane + 32] : -CUDART_INF_F;
+                    const float m_old = m_s[u];
+                    const float m_new = fmaxf(m_old, warp_max(fmaxf(s0, s1)));
+                    float p0 = 0.f, p1 = 0.f, corr = 1.f;
+                    if (m_new != -CUDART_INF_F) {
+                        p0 = expf(s0 - m_new);
+                        p1 = expf(s1 - m_new);
+                        corr = m_old == -CUDART_INF_F ? 0.f : expf(m_old - m_new);
+                    }
+                    const float sum = warp_sum(p0 + p1);
+                    __syncwarp();
+                    if (lane == 0) {
+                        m_s[u] = m_new;
+                        l_s[u] = l_s[u] * corr + sum;
+                        corr_s[u] = corr;
+                    }
+                    bf16* dst = p_s + (size_t)u * L.ps;
+                    if (lane < BN) dst[lane] = __float2bfloat16_rn(p0);
+                    if (lane + 32 < BN) dst[lane + 32] = __float2bfloat16_rn(p1);
+                }
+                __syncthreads();
+                // ---- values of the tile, into the keys' place
+                {
+                    const int cpr = dv / 8;
+                    for (int u = tid; u < G * BN * cpr; u += 256) {
+                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), j = j0 + jj;
+                        bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
+                        if (j <= last)
+                            cp_async16(smem_u32(dst), vpool + (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * dv + c8 * 8);
+                        else
+                            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);     // 0 x NaN is NaN
+                    }
+                    cp_async_wait_all();
+                }
+                __syncthreads();
+                // ---- 3: O = O corr + P V
+                {
+                    const int nts = dv / 8;
+                    for (int item = warp; item < H * nts; item += 8) {
+                        const int h = item / nts, nt = item % nts, kvh = h / rep;
+                        const int r = lane >> 2, c = nt * 8 + (lane & 3) * 2;
+                        float* op = o_s + ((size_t)h * QR + r) * L.os + c;
+                        const float c_lo = corr_s[h * QR + r];
+                        float acc[4] = {op[0] * c_lo, op[1] * c_lo, 0.f, 0.f};
+                        if (QR == 16) {
+                            const float c_hi = corr_s[h * QR + r + 8];
+                            acc[2] = op[8 * L.os] * c_hi;
+                            acc[3] = op[8 * L.os + 1] * c_hi;
+                        }
+                        const uint32_t a_base = smem_u32(p_s + ((size_t)h * QR + ((lane & 15) & (QR - 1))) * L.ps + (lane >> 4) * 8);
+                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + (lane & 15)) * L.kvs + nt * 8);
+                        for (int kk = 0; kk < BN / 16; ++kk) {
+                            uint32_t af[4], bfr[2];
+                            ldsm_x4(af, a_base + kk * 32);
+                            ldsm_x2_trans(bfr, b_base + (uint32_t)(kk * 16 * L.kvs * 2));
+                            mma_bf16(acc, af, bfr);
+                        }
+                        op[0] = acc[0];
+                        op[1] = acc[1];
+                        if (QR == 16) {
+                            op[8 * L.os] = acc[2];
+                            op[8 * L.os + 1] = acc[3];
+                        }
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        a = b;
+    }
+    __syncthreads();
+    // ---- the way out: divide, turn back by the row's position, round
+    const int hv = dv >> 1;
+    for (int u = tid; u < n_rows * H * hv; u += 256) {
+        const int m = u % hv, h = (u / hv) % H, r = u / (hv * H);
+        bf16* o_row = out + (size_t)(r0 + r) * H * dv + (size_t)h * dv;
+        float lo = 0.f, hi = 0.f;
+        if (slot_s[r] >= 0) {
+            const float inv_l = 1.f / l_s[h * QR + r];
+            const float* src = o_s + ((size_t)h * QR + r) * L.os;
+            if (inv_v != nullptr) {
+                float s, c;
+                sincosf((float)pos_s[r] * inv_v[m], &s, &c);
+                rotate_pair(src[m] * inv_l, src[m + hv] * inv_l, -s, c, lo, hi);
+            } else {
+                lo = src[m] * inv_l;
+                hi = src[m + hv] * inv_l;
+            }
+        }
+        o_row[m] = __float2bfloat16_rn(lo);
+        o_row[m + hv] = __float2bfloat16_rn(hi);
+    }
+}
+
 }  // namespace janis
 
 using namespace janis;
@@ -266,17 +555,72 @@ static int talk_plain_tile(int H, int G, int d, int dv, size_t* bytes) {
     return 0;
 }
 
+static int talk_kernel_choice = 1;        // 1: the tensor-core kernel where it fits; 0: the plain kernel always
+
+JANIS_EXPORT void janis_talk_attention_set_kernel(int which) { talk_kernel_choice = which; }
+
+// The shape the tensor-core kernel runs a step with, or qr = 0 when it does not take the sizes.
+static TalkMmaShape talk_mma_shape(int H, int G, int d, int dv, int one_row, size_t* bytes) {
+    TalkMmaShape sh = {};
+    if (H > 32 || d % 16 || dv % 8 || (dv & 1)) return sh;
+    static const int order[6][2] = {{16, 64}, {16, 32}, {8, 64}, {8, 32}, {16, 16}, {8, 16}};
+    for (int i = 0; i < 6; ++i) {
+        const int qr = order[i][0], bn = order[i][1];
+        if (one_row && qr != 8) continue;
+        const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, qr, bn);
+        if (L.total <= 220 * 1024) {
+            sh.qr = qr; sh.bn = bn; sh.rows = one_row ? 1 : qr;
+            *bytes = L.total;
+            return sh;
+        }
+    }
+    return sh;
+}
+
+template <int HMAX>
+static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_pos, const int* tok_seq, const int* seq_slot,
+                           const void* kpool, const void* vpool, const int* page_table, int table_stride,
+                           const float* talk, const float* inv_v, void* out, int T, const TalkMmaShape& sh, size_t bytes,
+                           cudaStream_t stream) {
+    static size_t most = 0;
+    if (bytes > most) {
+        cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<HMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+        if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
+        most = bytes;
+    }
+    const dim3 grid((T + sh.rows - 1) / sh.rows), block(256);
+    return launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
+                         q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
+                         table_stride, talk, inv_v, (bf16*)out, T, sh);
+}
+
 JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_elems, const int* tok_pos,
                                       const int* tok_seq, const int* seq_slot, const void* kpool, const void* vpool,
                                       const int* page_table, int table_stride, const float* talk, const float* inv_v,
                                       void* out, int T, int H, int G, int d, int dv, float scale, int block, int sink,
-                                      cudaStream_t stream) {
+                                      int one_row, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) return fail("talk_attention: %d query heads do not divide over %d key/value heads", H, G);
     if (d <= 0 || dv <= 0) return fail("talk_attention: key size %d, value size %d", d, dv);
     if (inv_v != nullptr && (dv & 1)) return fail("talk_attention: rotated values need an even size, found %d", dv);
     if (q_row_elems < H * d) return fail("talk_attention: query rows of %d elements are too short", q_row_elems);
     if (block < 0) return fail("talk_attention: block size %d", block);
+    if (dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
+        (((uintptr_t)q_rows | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0) {
+        size_t mma_bytes = 0;
+        TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
+        if (ms.qr) {
+            ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale;
+            if (H <= 8)
+                return talk_mma_launch<8>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
+                                          talk, inv_v, out, T, ms, mma_bytes, stream);
+            if (H <= 16)
+                return talk_mma_launch<16>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
+                                           talk, inv_v, out, T, ms, mma_bytes, stream);
+            return talk_mma_launch<32>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
+                                       talk, inv_v, out, T, ms, mma_bytes, stream);
+        }
+    }
     size_t bytes = 0;
     TalkShape sh;
     sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale;

@@ -137,7 +137,9 @@ def mixers():
         lib = build.mixers_library()
         P, I, F = c_void_p, c_int, c_float
         lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
-        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P]
+        lib.janis_talk_attention_set_kernel.argtypes = [I]
+        lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
@@ -773,12 +775,15 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, 
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
-                   d: int, dv: int, scale: float, block: int = 0, sink: bool = False):
+                   d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False):
     """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
     own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
     alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
     with sink, 1 is added to the softmax's denominator; with inv_v each head's output is turned back by the query's
-    position (the cached values were rotated by theirs).  q_rows [T, >= H d], out [T, H dv]."""
+    position (the cached values were rotated by theirs).  q_rows [T, >= H d], out [T, H dv].
+    bfloat16 with d a multiple of 16, dv a multiple of 8 and up to 32 heads runs on the tensor cores (a CTA per 16
+    or 8 rows of the step; one_row=True, for decode steps, gives every row a CTA of its own); everything else
+    runs the plain kernel, which is exact 32-bit for float32."""
     T = q_rows.shape[0]
     _t(q_rows, "q_rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
@@ -795,8 +800,13 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         page_table.data_ptr(), page_table.shape[1],
         _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None,
         _t(inv_v, "inv_v", torch.float32, (dv // 2,)) if inv_v is not None else None, out.data_ptr(), T, H, G, d, dv,
-        float(scale), int(block), 1 if sink else 0, _stream()))
+        float(scale), int(block), 1 if sink else 0, 1 if one_row else 0, _stream()))
     return out
+
+
+def talk_attention_set_kernel(which: int = 1) -> None:
+    """1: the tensor-core kernel where the sizes allow it (the default); 0: the plain kernel always.  For tests."""
+    mixers().janis_talk_attention_set_kernel(int(which))
 
 
 def gla_scan(rows, q_off: int, k_off: int, v_off: int, a_off: int, a2, a2_bias, seq_slot, seq_first_row, seq_start,

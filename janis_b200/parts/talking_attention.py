@@ -100,5 +100,5 @@ class TalkingHeadsAttention(Mixer):
                              kv.table if self.own_kv else None, store=self.own_kv)
         att = ws.buf("tattn.ctx", (T, H * dv), rt.dtype)
         ops.talk_attention(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, self.talk, inv_v, att,
-                           H, G, d, dv, self.scale, self.block, self.sink)
+                           H, G, d, dv, self.scale, self.block, self.sink, one_row=ctx.mode == "decode")
         return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

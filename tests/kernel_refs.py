@@ -347,7 +347,7 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G,
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
-                   block=0, sink=False):
+                   block=0, sink=False, one_row=False):
     T = q_rows.shape[0]
     rep = H // G
     for t in range(T):

@@ -227,7 +227,8 @@ def _paged(n_seq, lens, G, d, dv, dtype, seed, spare=3):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,d,dv,block,sink,talk,turn", [
     (4, 2, 32, 16, 24, True, True, True), (6, 6, 64, 32, 200, True, True, True), (3, 1, 24, 40, 1, True, False, False),
-    (8, 2, 64, 64, 128, False, True, True), (2, 2, 16, 8, 0, False, False, True), (5, 5, 8, 6, 7, True, True, False)])
+    (8, 2, 64, 64, 128, False, True, True), (2, 2, 16, 8, 0, False, False, True), (5, 5, 8, 6, 7, True, True, False),
+    (8, 4, 256, 256, 100, True, True, True), (20, 10, 32, 48, 65, True, True, True)])
 def test_attention_kernel_against_its_statement(dtype, H, G, d, dv, block, sink, talk, turn):
     """Queries at chosen positions (a block's first and last place, a page's border, far into the sequence) over
     scattered pages; one far key made to stand out for each query."""
@@ -255,12 +256,17 @@ def test_attention_kernel_against_its_statement(dtype, H, G, d, dv, block, sink,
     want = torch.zeros(T, H * dv, dtype=dtype)
     R.talk_attention(q, tok_pos, tok_seq, slots, kp, vp, table, M, inv_v, want, H, G, d, dv, 0.4, block, sink)
     dev = lambda x: x.cuda() if x is not None else None
-    got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
-    ops.talk_attention(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), dev(M), dev(inv_v), got,
-                       H, G, d, dv, 0.4, block, sink)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    err = (got.cpu().double() - want.double()).abs().max().item()
-    assert err <= tol * max(1.0, want.double().abs().max().item()), err
+    for which, one_row in ((1, False), (1, True), (0, False)):       # tensor cores (rows together, a row a CTA), plain
+        ops.talk_attention_set_kernel(which)
+        try:
+            got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
+            ops.talk_attention(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), dev(M),
+                               dev(inv_v), got, H, G, d, dv, 0.4, block, sink, one_row=one_row)
+        finally:
+            ops.talk_attention_set_kernel(1)
+        err = (got.cpu().double() - want.double()).abs().max().item()
+        assert err <= tol * max(1.0, want.double().abs().max().item()), (which, one_row, err)
 
 
 @GPU
