@@ -523,7 +523,7 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
         eng.stepper.step([StepEntry(slot, _tokens(model.vocab, prefill_tokens, 1), (prefill_tokens - 1,))])
     kernels["prefill_us"] = kt.totals_us()
     eng.free_slot(slot)
-    slots = fill(eng, [context - 1] * batch)
+    slots = fill(eng, [context - 2] * batch)
     graphs, eng.stepper.use_graphs = eng.stepper.use_graphs, False
     entries = [StepEntry(s, (1,), (0,)) for s in slots]
     eng.stepper.step(entries)

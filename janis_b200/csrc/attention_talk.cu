@@ -272,6 +272,7 @@ struct TalkMmaShape {
     int qr;             // rows of the operands kept (16 or 8)
     int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
     int bn;             // keys per tile (16, 32, 64)
+    int chunk;          // keys per CTA of a decode step whose rows are cut over grid.y CTAs (0: a row's keys in one CTA)
     float scale;
 };
 
@@ -294,7 +295,7 @@ __host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, in
     L.l = at;    at += (size_t)H * qr * 4;
     L.corr = at; at += (size_t)H * qr * 4;
     L.talk = at; at += (size_t)H * H * 4;
-    L.meta = at; at += 3 * 16 * 4;
+    L.meta = at; at += (3 * 16 + 64) * 4;
     L.total = at;
     return L;
 }
@@ -305,7 +306,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                           const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                           const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
                           const int* __restrict__ page_table, int table_stride, const float* __restrict__ talk,
-                          const float* __restrict__ inv_v, bf16* __restrict__ out, int n_tok, TalkMmaShape sh) {
+                          const float* __restrict__ inv_v, bf16* __restrict__ out, float* __restrict__ partial,
+                          int n_tok, TalkMmaShape sh) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = sh.H, G = sh.G, d = sh.d, dv = sh.dv, QR = sh.qr, BN = sh.bn, rep = H / G;
     const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, QR, BN);
@@ -321,6 +323,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     int* pos_s = reinterpret_cast<int*>(smem_raw + L.meta);
     int* seq_s = pos_s + 16;
     int* slot_s = pos_s + 32;
+    int* base_s = pos_s + 48;                  // where each key of the tile starts in the pools (in rows), -1 beyond the last
+    const bool split = sh.chunk > 0;           // the CTA leaves a partial result; the sink joins at the merge
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int r0 = blockIdx.x * sh.rows, n_rows = min(sh.rows, n_tok - r0);
     grid_dependents_launch();
@@ -335,8 +339,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         for (int u = tid; u < H * H; u += 256) talk_s[u] = talk[u];
     for (int u = tid; u < H * QR * L.os; u += 256) o_s[u] = 0.f;
     for (int u = tid; u < H * QR; u += 256) {
-        m_s[u] = sh.sink ? 0.f : -CUDART_INF_F;
-        l_s[u] = sh.sink ? 1.f : 0.f;
+        m_s[u] = sh.sink && !split ? 0.f : -CUDART_INF_F;
+        l_s[u] = sh.sink && !split ? 1.f : 0.f;
     }
     grid_dependency_wait();
     {   // queries: rows of the step, 16 bytes at a time; rows beyond the step's end are zero
@@ -355,17 +359,26 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         while (b < n_rows && seq_s[b] == seq_s[a]) ++b;
         const int slot = slot_s[a];
         if (slot >= 0) {
-            const int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
+            int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
+            if (split) {
+                first += (int)blockIdx.y * sh.chunk;
+                last = min(last, first + sh.chunk - 1);
+            }
             const int* table = page_table + (size_t)slot * table_stride;
             for (int j0 = first; j0 <= last; j0 += BN) {
                 // ---- keys of the tile
+                if (tid < BN) {
+                    const int j = j0 + tid;
+                    base_s[tid] = j <= last ? (table[j / JANIS_PAGE] * G) * JANIS_PAGE + j % JANIS_PAGE : -1;
+                }
+                __syncthreads();
                 {
                     const int cpr = d / 8;
                     for (int u = tid; u < G * BN * cpr; u += 256) {
-                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), j = j0 + jj;
+                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), at = base_s[jj];
                         bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
-                        if (j <= last)
-                            cp_async16(smem_u32(dst), kpool + (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * d + c8 * 8);
+                        if (at >= 0)
+                            cp_async16(smem_u32(dst), kpool + ((size_t)at + (size_t)g * JANIS_PAGE) * d + c8 * 8);
                         else
                             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
                     }
@@ -450,10 +463,10 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 {
                     const int cpr = dv / 8;
                     for (int u = tid; u < G * BN * cpr; u += 256) {
-                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), j = j0 + jj;
+                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), at = base_s[jj];
                         bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
-                        if (j <= last)
-                            cp_async16(smem_u32(dst), vpool + (((size_t)table[j / JANIS_PAGE] * G + g) * JANIS_PAGE + j % JANIS_PAGE) * dv + c8 * 8);
+                        if (at >= 0)
+                            cp_async16(smem_u32(dst), vpool + ((size_t)at + (size_t)g * JANIS_PAGE) * dv + c8 * 8);
                         else
                             *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);     // 0 x NaN is NaN
                     }
@@ -496,6 +509,15 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         a = b;
     }
     __syncthreads();
+    if (split) {
+        // the chunk's share of row r0: per head the unnormalised sums, then the maximum and the denominator
+        float* dst = partial + ((size_t)r0 * gridDim.y + blockIdx.y) * H * (dv + 2);
+        for (int u = tid; u < H * (dv + 2); u += 256) {
+            const int h = u / (dv + 2), c = u % (dv + 2);
+            dst[u] = c < dv ? o_s[(size_t)h * QR * L.os + c] : (c == dv ? m_s[h * QR] : l_s[h * QR]);
+        }
+        return;
+    }
     // ---- the way out: divide, turn back by the row's position, round
     const int hv = dv >> 1;
     for (int u = tid; u < n_rows * H * hv; u += 256) {
@@ -514,6 +536,51 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 hi = src[m + hv] * inv_l;
             }
         }
+        o_row[m] = __float2bfloat16_rn(lo);
+        o_row[m + hv] = __float2bfloat16_rn(hi);
+    }
+}
+
+// The chunks of a decode row put together, in ascending order: per head the maximum over the chunks (and the
+// sink's 0), the weights exp(m_c - M), the denominators and sums added, divided, turned back, rounded.
+__global__ void __launch_bounds__(128)
+talk_attention_merge_kernel(const float* __restrict__ partial, int n_chunks, const int* __restrict__ tok_pos,
+                            const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
+                            const float* __restrict__ inv_v, bf16* __restrict__ out, int H, int dv, int sink) {
+    const int t = blockIdx.x, tid = threadIdx.x;
+    grid_dependents_launch();
+    const int pos = tok_pos[t], slot = seq_slot[tok_seq[t]];
+    grid_dependency_wait();
+    const int hv = dv >> 1;
+    const float* base = partial + (size_t)t * n_chunks * H * (dv + 2);
+    for (int u = tid; u < H * hv; u += blockDim.x) {
+        const int h = u / hv, m = u % hv;
+        float lo = 0.f, hi = 0.f;
+        if (slot >= 0) {
+            const float* ph = base + (size_t)h * (dv + 2);
+            const size_t cs = (size_t)H * (dv + 2);
+            float M = sink ? 0.f : -CUDART_INF_F;
+            for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, ph[c * cs + dv]);
+            float Lsum = sink ? expf(-M) : 0.f, a0 = 0.f, a1 = 0.f;
+            for (int c = 0; c < n_chunks; ++c) {
+                const float mc = ph[c * cs + dv];
+                if (mc == -CUDART_INF_F) continue;
+                const float w = expf(mc - M);
+                Lsum = fmaf(w, ph[c * cs + dv + 1], Lsum);
+                a0 = fmaf(w, ph[c * cs + m], a0);
+                a1 = fmaf(w, ph[c * cs + m + hv], a1);
+            }
+            const float inv_l = 1.f / Lsum;
+            if (inv_v != nullptr) {
+                float s, c;
+                sincosf((float)pos * inv_v[m], &s, &c);
+                rotate_pair(a0 * inv_l, a1 * inv_l, -s, c, lo, hi);
+            } else {
+                lo = a0 * inv_l;
+                hi = a1 * inv_l;
+            }
+        }
+        bf16* o_row = out + (size_t)t * H * dv + (size_t)h * dv;
         o_row[m] = __float2bfloat16_rn(lo);
         o_row[m + hv] = __float2bfloat16_rn(hi);
     }
@@ -580,25 +647,30 @@ static TalkMmaShape talk_mma_shape(int H, int G, int d, int dv, int one_row, siz
 template <int HMAX>
 static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_pos, const int* tok_seq, const int* seq_slot,
                            const void* kpool, const void* vpool, const int* page_table, int table_stride,
-                           const float* talk, const float* inv_v, void* out, int T, const TalkMmaShape& sh, size_t bytes,
-                           cudaStream_t stream) {
+                           const float* talk, const float* inv_v, void* out, float* partial, int n_chunks, int T,
+                           const TalkMmaShape& sh, size_t bytes, cudaStream_t stream) {
     static size_t most = 0;
     if (bytes > most) {
         cudaError_t e = cudaFuncSetAttribute(talk_attention_mma_kernel<HMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
         if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
         most = bytes;
     }
-    const dim3 grid((T + sh.rows - 1) / sh.rows), block(256);
-    return launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
-                         q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
-                         table_stride, talk, inv_v, (bf16*)out, T, sh);
+    const dim3 grid((T + sh.rows - 1) / sh.rows, sh.chunk > 0 ? n_chunks : 1), block(256);
+    if (launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
+                      q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
+                      table_stride, talk, inv_v, (bf16*)out, partial, T, sh))
+        return 1;
+    if (sh.chunk == 0) return 0;
+    return launch_kernel("talk_attention_merge", talk_attention_merge_kernel, dim3(T), dim3(128), 0, stream, 1,
+                         (const float*)partial, n_chunks, tok_pos, tok_seq, seq_slot, inv_v, (bf16*)out, sh.H, sh.dv, sh.sink);
 }
 
 JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_elems, const int* tok_pos,
                                       const int* tok_seq, const int* seq_slot, const void* kpool, const void* vpool,
                                       const int* page_table, int table_stride, const float* talk, const float* inv_v,
                                       void* out, int T, int H, int G, int d, int dv, float scale, int block, int sink,
-                                      int one_row, cudaStream_t stream) {
+                                      int one_row, int max_keys, int n_chunks, float* partial, long long partial_floats,
+                                      cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) return fail("talk_attention: %d query heads do not divide over %d key/value heads", H, G);
     if (d <= 0 || dv <= 0) return fail("talk_attention: key size %d, value size %d", d, dv);
@@ -611,14 +683,21 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
         TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
         if (ms.qr) {
             ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale;
+            if (one_row && n_chunks > 1 && max_keys > 0 && partial != nullptr) {
+                // a decode row's keys over n_chunks CTAs, each a whole number of tiles
+                if (partial_floats < (long long)T * n_chunks * H * (dv + 2))
+                    return fail("talk_attention: scratch of %lld floats is too small for %d rows in %d chunks", partial_floats, T, n_chunks);
+                const int per = (max_keys + n_chunks - 1) / n_chunks;
+                ms.chunk = (per + ms.bn - 1) / ms.bn * ms.bn;
+            }
             if (H <= 8)
                 return talk_mma_launch<8>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                          talk, inv_v, out, T, ms, mma_bytes, stream);
+                                          talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
             if (H <= 16)
                 return talk_mma_launch<16>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                           talk, inv_v, out, T, ms, mma_bytes, stream);
+                                           talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
             return talk_mma_launch<32>(q_rows, q_row_elems, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, table_stride,
-                                       talk, inv_v, out, T, ms, mma_bytes, stream);
+                                       talk, inv_v, out, partial, n_chunks, T, ms, mma_bytes, stream);
         }
     }
     size_t bytes = 0;

@@ -1,6 +1,6 @@
 // Gated linear attention: a recurrent mixer with a matrix of state per head.
 //
-//   a_t  = sigmoid(z_t)^(1/tau),   z_t = A2 (a1_t) + b        one decay per key channel (a1_t: a low-rank projection)
+//   a_t  = sigmoid(z_t + b)^(1/tau)                           one decay per key channel (z_t: a projection of the input)
 //   S_t  = diag(a_t) S_{t-1} + k_t v_t^T                      S: [d, dv] float per head and sequence
 //   o_t  = S_t^T (q_t * q_scale)
 //
@@ -18,8 +18,8 @@ constexpr int GLA_TT = 16;         // tokens staged per round
 
 struct GlaRows {
     int row_elems;                 // elements per row of the projected step
-    int q_off, k_off, v_off, a_off;    // where q [H, d], k [H, d], v [H, dv] and the low-rank a1 [r] start in a row
-    int H, d, dv, r;
+    int q_off, k_off, v_off;       // where q [H, d], k [H, d] and v [H, dv] start in a row
+    int H, d, dv;
     float q_scale, inv_tau;
 };
 
@@ -30,17 +30,16 @@ __device__ __forceinline__ float log_sigmoid(float z) {       // -softplus(-z), 
 // grid (sequences, heads, ceil(dv / GLA_COLS)); 128 threads: thread = (column, ks), ks fastest.
 template <typename T, int DPT>
 __global__ void __launch_bounds__(GLA_COLS * GLA_KS)
-gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ a2, const T* __restrict__ a2_bias,
+gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_rows, const T* __restrict__ z_bias,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state,
                 float* __restrict__ o_out) {
     extern __shared__ float smem[];
-    const int d = g.d, dv = g.dv, r = g.r, H = g.H;
+    const int d = g.d, dv = g.dv, H = g.H;
     float* q_s = smem;                       // [TT, d]
     float* k_s = q_s + GLA_TT * d;           // [TT, d]
     float* a_s = k_s + GLA_TT * d;           // [TT, d]
     float* v_s = a_s + GLA_TT * d;           // [TT, GLA_COLS]
-    float* a1_s = v_s + GLA_TT * GLA_COLS;   // [TT, r]
     const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int tid = threadIdx.x, ks = tid % GLA_KS, col = col0 + tid / GLA_KS;
     const bool live = col < dv;
@@ -58,27 +57,17 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ a2,
     for (int t0 = 0; t0 < n_tok; t0 += GLA_TT) {
         const int tt_n = min(GLA_TT, n_tok - t0);
         __syncthreads();
-        for (int u = tid; u < tt_n * r; u += blockDim.x) {
-            const int tt = u / r, rr = u % r;
-            a1_s[u] = to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.a_off + rr]);
-        }
         for (int u = tid; u < tt_n * d; u += blockDim.x) {
             const int tt = u / d, c = u % d;
             const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
             q_s[u] = to_float(row[g.q_off + h * d + c]) * g.q_scale;
             k_s[u] = to_float(row[g.k_off + h * d + c]);
+            const float z = to_float(z_rows[(size_t)(row0 + t0 + tt) * H * d + h * d + c]) + to_float(z_bias[h * d + c]);
+            a_s[u] = expf(log_sigmoid(z) * g.inv_tau);
         }
         for (int u = tid; u < tt_n * GLA_COLS; u += blockDim.x) {
             const int tt = u / GLA_COLS, c = col0 + u % GLA_COLS;
             v_s[u] = c < dv ? to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.v_off + h * dv + c]) : 0.f;
-        }
-        __syncthreads();
-        for (int u = tid; u < tt_n * d; u += blockDim.x) {
-            const int tt = u / d, c = u % d;
-            const T* w = a2 + (size_t)(h * d + c) * r;
-            float z = to_float(a2_bias[h * d + c]);
-            for (int rr = 0; rr < r; ++rr) z = fmaf(to_float(w[rr]), a1_s[tt * r + rr], z);
-            a_s[u] = expf(log_sigmoid(z) * g.inv_tau);
         }
         __syncthreads();
         for (int tt = 0; tt < tt_n; ++tt) {
@@ -86,15 +75,16 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ a2,
             const float* qq = q_s + tt * d;
             const float* kk = k_s + tt * d;
             const float* aa = a_s + tt * d;
-            float acc = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};           // four chains, added in a fixed order
 #pragma unroll
             for (int ii = 0; ii < DPT; ++ii) {
                 const int i = ks + GLA_KS * ii;
                 if (i < d) {
                     S[ii] = fmaf(aa[i], S[ii], kk[i] * v);
-                    acc = fmaf(S[ii], qq[i], acc);
+                    part[ii & 3] = fmaf(S[ii], qq[i], part[ii & 3]);
                 }
             }
+            float acc = (part[0] + part[1]) + (part[2] + part[3]);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             if (ks == 0 && live) o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = acc;
@@ -145,11 +135,11 @@ JANIS_EXPORT void janis_mixers_set_overlap(int on) { overlap_launches() = on ? 1
 JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }
 
 template <typename T>
-static int gla_scan_launch(const void* rows, const GlaRows& g, const void* a2, const void* a2_bias, const int* seq_slot,
+static int gla_scan_launch(const void* rows, const GlaRows& g, const void* z_rows, const void* z_bias, const int* seq_slot,
                            const int* seq_first_row, const int* seq_start, const int* seq_end, float* state, float* o_out,
                            int n_seq, cudaStream_t stream) {
     const dim3 grid(n_seq, g.H, (g.dv + GLA_COLS - 1) / GLA_COLS), block(GLA_COLS * GLA_KS);
-    const size_t smem = ((size_t)GLA_TT * (3 * g.d + GLA_COLS + g.r)) * sizeof(float);
+    const size_t smem = ((size_t)GLA_TT * (3 * g.d + GLA_COLS)) * sizeof(float);
 #define JANIS_GLA_CASE(DPT)                                                                                            \
     if (g.d <= GLA_KS * DPT) {                                                                                         \
         if (smem > 48 * 1024) {                                                                                        \
@@ -157,7 +147,7 @@ static int gla_scan_launch(const void* rows, const GlaRows& g, const void* a2, c
             if (e != cudaSuccess) return fail("gla_scan: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e)); \
         }                                                                                                              \
         return launch_kernel("gla_scan", gla_scan_kernel<T, DPT>, grid, block, smem, stream, 1, (const T*)rows, g,     \
-                             (const T*)a2, (const T*)a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out); \
+                             (const T*)z_rows, (const T*)z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out); \
     }
     JANIS_GLA_CASE(8)
     JANIS_GLA_CASE(16)
@@ -167,21 +157,21 @@ static int gla_scan_launch(const void* rows, const GlaRows& g, const void* a2, c
     return fail("gla_scan: key size %d is above %d", g.d, GLA_KS * 64);
 }
 
-JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off, int a_off,
-                                const void* a2, const void* a2_bias, const int* seq_slot, const int* seq_first_row,
+JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off,
+                                const void* z_rows, const void* z_bias, const int* seq_slot, const int* seq_first_row,
                                 const int* seq_start, const int* seq_end, float* state, float* o_out, int n_seq, int H,
-                                int d, int dv, int r, float q_scale, float tau, cudaStream_t stream) {
+                                int d, int dv, float q_scale, float tau, cudaStream_t stream) {
     if (n_seq <= 0) return 0;
-    if (H <= 0 || d <= 0 || dv <= 0 || r <= 0) return fail("gla_scan: sizes %d heads, %d x %d, rank %d", H, d, dv, r);
+    if (H <= 0 || d <= 0 || dv <= 0) return fail("gla_scan: sizes %d heads, %d x %d", H, d, dv);
     if (!(tau > 0.f)) return fail("gla_scan: tau must be positive");
     if (H > 65535) return fail("gla_scan: too many heads (%d)", H);
     GlaRows g;
-    g.row_elems = row_elems; g.q_off = q_off; g.k_off = k_off; g.v_off = v_off; g.a_off = a_off;
-    g.H = H; g.d = d; g.dv = dv; g.r = r; g.q_scale = q_scale; g.inv_tau = 1.0f / tau;
+    g.row_elems = row_elems; g.q_off = q_off; g.k_off = k_off; g.v_off = v_off;
+    g.H = H; g.d = d; g.dv = dv; g.q_scale = q_scale; g.inv_tau = 1.0f / tau;
     if (dtype == JANIS_F32)
-        return gla_scan_launch<float>(rows, g, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+        return gla_scan_launch<float>(rows, g, z_rows, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
     if (dtype == JANIS_BF16)
-        return gla_scan_launch<bf16>(rows, g, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+        return gla_scan_launch<bf16>(rows, g, z_rows, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
     return fail("gla_scan: unknown dtype %d", dtype);
 }
 

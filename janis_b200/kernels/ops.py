@@ -137,10 +137,10 @@ def mixers():
         lib = build.mixers_library()
         P, I, F = c_void_p, c_int, c_float
         lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
-        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
-        lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, I, F, F, P]
+        lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
         lib.janis_mixers_set_overlap.restype = None
@@ -775,7 +775,8 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, 
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
-                   d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False):
+                   d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False,
+                   max_keys: int = 0, n_chunks: int = 1, scratch=None):
     """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
     own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
     alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
@@ -783,7 +784,9 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
     position (the cached values were rotated by theirs).  q_rows [T, >= H d], out [T, H dv].
     bfloat16 with d a multiple of 16, dv a multiple of 8 and up to 32 heads runs on the tensor cores (a CTA per 16
     or 8 rows of the step; one_row=True, for decode steps, gives every row a CTA of its own); everything else
-    runs the plain kernel, which is exact 32-bit for float32."""
+    runs the plain kernel, which is exact 32-bit for float32.  A decode step on the tensor cores may cut every row's
+    keys over n_chunks CTAs (max_keys: a bound on the keys a row sees; scratch: float32, at least
+    `talk_attention_scratch_floats`) whose shares a second kernel puts together."""
     T = q_rows.shape[0]
     _t(q_rows, "q_rows", _FLOATS, (T, None))
     n_pages = kpool.shape[0]
@@ -800,8 +803,15 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         page_table.data_ptr(), page_table.shape[1],
         _t(talk, "talk", torch.float32, (H, H)) if talk is not None else None,
         _t(inv_v, "inv_v", torch.float32, (dv // 2,)) if inv_v is not None else None, out.data_ptr(), T, H, G, d, dv,
-        float(scale), int(block), 1 if sink else 0, 1 if one_row else 0, _stream()))
+        float(scale), int(block), 1 if sink else 0, 1 if one_row else 0, int(max_keys), int(n_chunks),
+        _t(scratch, "scratch", torch.float32) if scratch is not None else None,
+        scratch.numel() if scratch is not None else 0, _stream()),
+        kernels=2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1)
     return out
+
+
+def talk_attention_scratch_floats(T: int, n_chunks: int, H: int, dv: int) -> int:
+    return T * n_chunks * H * (dv + 2) if n_chunks > 1 else 0
 
 
 def talk_attention_set_kernel(which: int = 1) -> None:
@@ -809,17 +819,17 @@ def talk_attention_set_kernel(which: int = 1) -> None:
     mixers().janis_talk_attention_set_kernel(int(which))
 
 
-def gla_scan(rows, q_off: int, k_off: int, v_off: int, a_off: int, a2, a2_bias, seq_slot, seq_first_row, seq_start,
-             seq_end, state, o_out, n_seq: int, H: int, d: int, dv: int, r: int, q_scale: float, tau: float):
+def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state,
+             o_out, n_seq: int, H: int, d: int, dv: int, q_scale: float, tau: float):
     """The recurrence of gated linear attention over the tokens each sequence brings to the step, in order:
-    a = sigmoid(a2 a1 + a2_bias)^(1/tau) per key channel, S = diag(a) S + k v^T, o = S^T (q q_scale).
-    rows [T, width] holds the projections (q [H, d] at q_off, k at k_off, v [H, dv] at v_off, a1 [r] at a_off);
-    state float32 [slots, H, d, dv] is read and written back for sequences whose slot is >= 0; o_out float32
-    [T, H dv]."""
+    a = sigmoid(z + z_bias)^(1/tau) per key channel, S = diag(a) S + k v^T, o = S^T (q q_scale).
+    rows [T, width] holds the projections (q [H, d] at q_off, k at k_off, v [H, dv] at v_off), z [T, H d] the
+    projected decay logits; state float32 [slots, H, d, dv] is read and written back for sequences whose slot is
+    >= 0; o_out float32 [T, H dv]."""
     T, width = rows.shape
     _t(rows, "rows", _FLOATS, (T, None))
-    _t(a2, "a2", rows.dtype, (H * d, r))
-    _t(a2_bias, "a2_bias", rows.dtype, (H * d,))
+    _t(z, "z", rows.dtype, (T, H * d))
+    _t(z_bias, "z_bias", rows.dtype, (H * d,))
     _t(state, "state", torch.float32, (None, H, d, dv))
     _t(o_out, "o_out", torch.float32, (T, H * dv))
     for name, tab in (("seq_slot", seq_slot), ("seq_first_row", seq_first_row), ("seq_start", seq_start), ("seq_end", seq_end)):
@@ -827,9 +837,9 @@ def gla_scan(rows, q_off: int, k_off: int, v_off: int, a_off: int, a2, a2_bias, 
         if tab.numel() < n_seq:
             raise KernelError(f"gla_scan: {name} shorter than the step's sequences")
     lib = mixers()
-    _check(lib, lib.janis_gla_scan(rows.data_ptr(), _DT[rows.dtype], width, q_off, k_off, v_off, a_off, a2.data_ptr(),
-                                   a2_bias.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
-                                   seq_end.data_ptr(), state.data_ptr(), o_out.data_ptr(), n_seq, H, d, dv, r,
+    _check(lib, lib.janis_gla_scan(rows.data_ptr(), _DT[rows.dtype], width, q_off, k_off, v_off, z.data_ptr(),
+                                   z_bias.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
+                                   seq_end.data_ptr(), state.data_ptr(), o_out.data_ptr(), n_seq, H, d, dv,
                                    float(q_scale), float(tau), _stream()))
     return o_out
 

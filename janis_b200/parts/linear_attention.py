@@ -7,8 +7,9 @@ With y the mixer's input, per head (d key channels, dv value channels):
     S <- diag(a) S + k v^T,   o = S^T q               S starts at zero and lives in the cache, in float32
 
 then each head's o is RMS-normed over its dv channels (one weight vector for all heads), the heads are put side by
-side, multiplied by silu(Wg y) and projected by Wo.  The five projections of y are one product over the rows
-q | k | v | g | a1 concatenated at load.  Decays, the state and o are float32 whatever the activations are.
+side, multiplied by silu(Wg y) and projected by Wo.  Four projections of y are one product over the rows
+q | k | v | g concatenated at load; the decay logits are two small products of their own.  Decays (from the
+logits on), the state and o are float32 whatever the activations are.
 
 The state is a fixed-size part of a cache line (`StateNeed`): a step loads it, runs its tokens in order and
 writes it back, so a prompt, a prompt that continues and a decode step are one code path; sequences without a
@@ -41,7 +42,7 @@ class GatedLinearAttention(Mixer):
         self.q_scale = float(q_scale) if q_scale is not None else key_dim ** -0.5
         self.names = dict(names)
         self.init_std = init_std
-        self.w_in = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
+        self.w_in = self.w_a1 = self.w_a2 = self.b_a2 = self.w_norm = self.w_o = None
 
     def tensor_specs(self):
         H, d, dv, W, s, n = self.n_heads, self.key_dim, self.value_dim, self.hidden, self.init_std, self.names
@@ -59,11 +60,12 @@ class GatedLinearAttention(Mixer):
 
     def load(self, store, rt: Runtime):
         n = self.names
-        parts = [store.get(n[k], rt.dtype) for k in ("q", "k", "v", "g", "a1")]
-        self.rank = int(parts[4].shape[0])
+        parts = [store.get(n[k], rt.dtype) for k in ("q", "k", "v", "g")]
         self.w_in = torch.cat(parts, dim=0).contiguous()
         del parts
-        store.drop(*(n[k] for k in ("q", "k", "v", "g", "a1")))
+        store.drop(*(n[k] for k in ("q", "k", "v", "g")))
+        self.w_a1 = store.get(n["a1"], rt.dtype).contiguous()
+        self.rank = int(self.w_a1.shape[0])
         self.w_a2 = store.get(n["a2"], rt.dtype).contiguous()
         if tuple(self.w_a2.shape) != (self.n_heads * self.key_dim, self.rank):
             raise ValueError(f"{n['a2']}: shape {tuple(self.w_a2.shape)} does not continue the rank {self.rank} of {n['a1']}")
@@ -77,12 +79,14 @@ class GatedLinearAttention(Mixer):
         if not st.write:
             raise ValueError("a recurrent state has one writer: a gated-linear-attention layer cannot read another's line")
         T, H, d, dv, r = ctx.n_tok, self.n_heads, self.key_dim, self.value_dim, self.rank
-        q_off, k_off, v_off, g_off, a_off = 0, H * d, 2 * H * d, 2 * H * d + H * dv, 2 * H * d + 2 * H * dv
-        rows = ws.buf("gla.rows", (T, a_off + r), rt.dtype)
+        q_off, k_off, v_off, g_off = 0, H * d, 2 * H * d, 2 * H * d + H * dv
+        rows = ws.buf("gla.rows", (T, g_off + H * dv), rt.dtype)
         rt.linear(x, self.w_in, rows)
+        z = rt.linear(rt.linear(x, self.w_a1, ws.buf("gla.a1", (T, r), rt.dtype)), self.w_a2,
+                      ws.buf("gla.z", (T, H * d), rt.dtype))
         o = ws.buf("gla.o", (T, H * dv), torch.float32)
-        ops.gla_scan(rows, q_off, k_off, v_off, a_off, self.w_a2, self.b_a2, ctx.seq_slot, ctx.seq_first_row,
-                     ctx.seq_start, ctx.seq_end, st.data, o, ctx.n_seq, H, d, dv, r, self.q_scale, self.tau)
+        ops.gla_scan(rows, q_off, k_off, v_off, z, self.b_a2, ctx.seq_slot, ctx.seq_first_row, ctx.seq_start,
+                     ctx.seq_end, st.data, o, ctx.n_seq, H, d, dv, self.q_scale, self.tau)
         y = ws.buf("gla.y", (T, H * dv), rt.dtype)
         ops.head_norm_gate(o, rows, g_off, self.w_norm, self.norm_eps, y, H, dv)
         return rt.linear(y, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

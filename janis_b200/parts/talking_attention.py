@@ -99,6 +99,16 @@ class TalkingHeadsAttention(Mixer):
                              inv_v, H, G, d, dv, kv.k if self.own_kv else None, kv.v if self.own_kv else None,
                              kv.table if self.own_kv else None, store=self.own_kv)
         att = ws.buf("tattn.ctx", (T, H * dv), rt.dtype)
+        decode = ctx.mode == "decode"
+        max_keys, n_chunks, scratch = 0, 1, None
+        if decode:
+            # a decode row's keys over several CTAs when the rows alone would leave most of the GPU idle: about an
+            # SM's worth of CTAs in all, none with fewer than 128 keys (the bound on the lengths is the host's)
+            max_keys = min(self.block, ctx.len_bound) if self.block else ctx.len_bound
+            n_chunks = max(1, min(rt.sm_count // max(T, 1), -(-max_keys // 128), 64))
+            n = ops.talk_attention_scratch_floats(T, n_chunks, H, dv)
+            scratch = ws.buf("tattn.partial", (n,), torch.float32) if n else None
         ops.talk_attention(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, self.talk, inv_v, att,
-                           H, G, d, dv, self.scale, self.block, self.sink, one_row=ctx.mode == "decode")
+                           H, G, d, dv, self.scale, self.block, self.sink, one_row=decode, max_keys=max_keys,
+                           n_chunks=n_chunks, scratch=scratch)
         return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

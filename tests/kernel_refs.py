@@ -347,7 +347,7 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G,
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
-                   block=0, sink=False, one_row=False):
+                   block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None):
     T = q_rows.shape[0]
     rep = H // G
     for t in range(T):
@@ -373,8 +373,12 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
     return out
 
 
-def gla_scan(rows, q_off, k_off, v_off, a_off, a2, a2_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out,
-             n_seq, H, d, dv, r, q_scale, tau):
+def talk_attention_scratch_floats(T, n_chunks, H, dv):
+    return T * n_chunks * H * (dv + 2) if n_chunks > 1 else 0
+
+
+def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, H,
+             d, dv, q_scale, tau):
     for s in range(n_seq):
         slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
         if n <= 0:
@@ -385,8 +389,7 @@ def gla_scan(rows, q_off, k_off, v_off, a_off, a2, a2_bias, seq_slot, seq_first_
             q = row[q_off:q_off + H * d].view(H, d) * q_scale
             k = row[k_off:k_off + H * d].view(H, d)
             v = row[v_off:v_off + H * dv].view(H, dv)
-            z = a2.double() @ row[a_off:a_off + r] + a2_bias.double()
-            a = torch.exp(torch.nn.functional.logsigmoid(z) / tau).view(H, d)
+            a = torch.exp(torch.nn.functional.logsigmoid(z[t].double() + z_bias.double()) / tau).view(H, d)
             S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
             o_out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).float()
         if slot >= 0:

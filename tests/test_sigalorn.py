@@ -257,16 +257,20 @@ def test_attention_kernel_against_its_statement(dtype, H, G, d, dv, block, sink,
     R.talk_attention(q, tok_pos, tok_seq, slots, kp, vp, table, M, inv_v, want, H, G, d, dv, 0.4, block, sink)
     dev = lambda x: x.cuda() if x is not None else None
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    for which, one_row in ((1, False), (1, True), (0, False)):       # tensor cores (rows together, a row a CTA), plain
+    # tensor cores (rows together; a row a CTA; a row's keys over 3 and over 7 CTAs), then the plain kernel
+    for which, one_row, chunks in ((1, False, 1), (1, True, 1), (1, True, 3), (1, True, 7), (0, False, 1)):
         ops.talk_attention_set_kernel(which)
         try:
             got = torch.full((T, H * dv), float("nan"), dtype=dtype, device="cuda")
+            n = ops.talk_attention_scratch_floats(T, chunks, H, dv)
+            scratch = torch.full((n,), float("nan"), device="cuda") if n else None
             ops.talk_attention(dev(q), dev(tok_pos), dev(tok_seq), dev(slots), dev(kp), dev(vp), dev(table), dev(M),
-                               dev(inv_v), got, H, G, d, dv, 0.4, block, sink, one_row=one_row)
+                               dev(inv_v), got, H, G, d, dv, 0.4, block, sink, one_row=one_row,
+                               max_keys=min(block, 300) if block else 300, n_chunks=chunks, scratch=scratch)
         finally:
             ops.talk_attention_set_kernel(1)
         err = (got.cpu().double() - want.double()).abs().max().item()
-        assert err <= tol * max(1.0, want.double().abs().max().item()), (which, one_row, err)
+        assert err <= tol * max(1.0, want.double().abs().max().item()), (which, one_row, chunks, err)
 
 
 @GPU
@@ -304,9 +308,8 @@ def test_rotation_and_cache_write_against_their_statement(dtype, H, G, d, dv, ro
 
 @GPU
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,d,dv,r,tau", [(2, 16, 24, 8, 8.0), (1, 40, 48, 24, 32.0), (3, 8, 8, 4, 1.0), (2, 128, 72, 16, 16.0),
-                                          (1, 200, 32, 2, 4.0)])
-def test_recurrence_kernel_against_its_statement(dtype, H, d, dv, r, tau):
+@pytest.mark.parametrize("H,d,dv,tau", [(2, 16, 24, 8.0), (1, 40, 48, 32.0), (3, 8, 8, 1.0), (2, 128, 72, 16.0), (1, 200, 32, 4.0)])
+def test_recurrence_kernel_against_its_statement(dtype, H, d, dv, tau):
     """Sequences of 1, 17 and 40 tokens (one without a slot), the second step continuing from the state the
     first one left; then the head norm and gate."""
     from janis_b200.kernels import ops
@@ -314,23 +317,23 @@ def test_recurrence_kernel_against_its_statement(dtype, H, d, dv, r, tau):
     g = torch.Generator().manual_seed(6)
     lens = [1, 17, 40]
     T = sum(lens)
-    width = 2 * H * d + 2 * H * dv + r
-    a2 = (0.3 * torch.randn(H * d, r, generator=g)).to(dtype)
+    width = 2 * H * d + 2 * H * dv
     b2 = (1.0 + torch.randn(H * d, generator=g)).to(dtype)
     state_cpu = torch.zeros(4, H, d, dv)
     state_dev = state_cpu.clone().cuda()
     slots = torch.tensor([2, -1, 0], dtype=torch.int32)
     first = torch.tensor([0, 1, 18], dtype=torch.int32)
     start = torch.zeros(3, dtype=torch.int32)
-    offs = (0, H * d, 2 * H * d, 2 * H * d + 2 * H * dv)
+    offs = (0, H * d, 2 * H * d)
     for step in range(2):
         rows = torch.randn(T, width, generator=g).to(dtype)
+        z = (2.0 * torch.randn(T, H * d, generator=g)).to(dtype)
         end = start + torch.tensor(lens, dtype=torch.int32)
         want = torch.zeros(T, H * dv)
-        R.gla_scan(rows, *offs, a2, b2, slots, first, start, end, state_cpu, want, 3, H, d, dv, r, d ** -0.5, tau)
+        R.gla_scan(rows, *offs, z, b2, slots, first, start, end, state_cpu, want, 3, H, d, dv, d ** -0.5, tau)
         got = torch.full((T, H * dv), float("nan"), device="cuda")
-        ops.gla_scan(rows.cuda(), *offs, a2.cuda(), b2.cuda(), slots.cuda(), first.cuda(), start.cuda(), end.cuda(),
-                     state_dev, got, 3, H, d, dv, r, d ** -0.5, tau)
+        ops.gla_scan(rows.cuda(), *offs, z.cuda(), b2.cuda(), slots.cuda(), first.cuda(), start.cuda(), end.cuda(),
+                     state_dev, got, 3, H, d, dv, d ** -0.5, tau)
         scale = max(1.0, want.abs().max().item())
         assert (got.cpu() - want).abs().max().item() <= 2e-5 * scale
         assert (state_dev.cpu() - state_cpu).abs().max().item() <= 2e-5 * max(1.0, state_cpu.abs().max().item())
