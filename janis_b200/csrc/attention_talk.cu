@@ -326,7 +326,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     int* base_s = pos_s + 48;                  // where each key of the tile starts in the pools (in rows), -1 beyond the last
     const bool split = sh.chunk > 0;           // the CTA leaves a partial result; the sink joins at the merge
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int r0 = blockIdx.x * sh.rows, n_rows = min(sh.rows, n_tok - r0);
+    // the last rows of a prompt see the most keys: they start first
+    const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * sh.rows, n_rows = min(sh.rows, n_tok - r0);
     grid_dependents_launch();
     if (tid < 16) {
         const bool in = tid < n_rows;
@@ -385,28 +386,41 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     cp_async_wait_all();
                 }
                 __syncthreads();
-                // ---- 1: raw scores of every head
+                // ---- 1: raw scores of every head; a warp takes a head and up to four tiles of 8 keys, which share
+                //         the queries' fragments and run as four independent chains
                 {
-                    const int nts = BN / 8;
-                    for (int item = warp; item < H * nts; item += 8) {
-                        const int g = item / nts, nt = item % nts, kvh = g / rep;
-                        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+                    const int nts = BN / 8, groups = (nts + 3) / 4;
+                    for (int unit = warp; unit < H * groups; unit += 8) {
+                        const int g = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = g / rep;
+                        float acc[4][4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
                         const uint32_t a_base = smem_u32(q_s + ((size_t)g * QR + ((lane & 15) & (QR - 1))) * L.qs + (lane >> 4) * 8);
-                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + nt * 8 + (lane & 7)) * L.kvs + ((lane >> 3) & 1) * 8);
+                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + nt0 * 8 + (lane & 7)) * L.kvs + ((lane >> 3) & 1) * 8);
+                        const uint32_t b_step = (uint32_t)(8 * L.kvs * 2);
                         for (int kk = 0; kk < d / 16; ++kk) {
-                            uint32_t af[4], bfr[2];
+                            uint32_t af[4];
                             ldsm_x4(af, a_base + kk * 32);
-                            ldsm_x2(bfr, b_base + kk * 32);
-                            mma_bf16(acc, af, bfr);
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (t < n_here) {
+                                    uint32_t bfr[2];
+                                    ldsm_x2(bfr, b_base + t * b_step + kk * 32);
+                                    mma_bf16(acc[t], af, bfr);
+                                }
                         }
-                        const int r = lane >> 2, c = nt * 8 + (lane & 3) * 2;
-                        float* dst = raw_s + ((size_t)g * QR + r) * L.rs + c;
-                        dst[0] = acc[0] * sh.scale;
-                        dst[1] = acc[1] * sh.scale;
-                        if (QR == 16) {
-                            dst[8 * L.rs] = acc[2] * sh.scale;
-                            dst[8 * L.rs + 1] = acc[3] * sh.scale;
-                        }
+                        const int r = lane >> 2;
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            if (t < n_here) {
+                                float* dst = raw_s + ((size_t)g * QR + r) * L.rs + (nt0 + t) * 8 + (lane & 3) * 2;
+                                dst[0] = acc[t][0] * sh.scale;
+                                dst[1] = acc[t][1] * sh.scale;
+                                if (QR == 16) {
+                                    dst[8 * L.rs] = acc[t][2] * sh.scale;
+                                    dst[8 * L.rs + 1] = acc[t][3] * sh.scale;
+                                }
+                            }
                     }
                 }
                 __syncthreads();
@@ -473,34 +487,51 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     cp_async_wait_all();
                 }
                 __syncthreads();
-                // ---- 3: O = O corr + P V
+                // ---- 3: O = O corr + P V; a warp takes a head and up to four tiles of 8 value columns, which share
+                //         P's fragments and run as four independent chains
                 {
-                    const int nts = dv / 8;
-                    for (int item = warp; item < H * nts; item += 8) {
-                        const int h = item / nts, nt = item % nts, kvh = h / rep;
-                        const int r = lane >> 2, c = nt * 8 + (lane & 3) * 2;
-                        float* op = o_s + ((size_t)h * QR + r) * L.os + c;
-                        const float c_lo = corr_s[h * QR + r];
-                        float acc[4] = {op[0] * c_lo, op[1] * c_lo, 0.f, 0.f};
-                        if (QR == 16) {
-                            const float c_hi = corr_s[h * QR + r + 8];
-                            acc[2] = op[8 * L.os] * c_hi;
-                            acc[3] = op[8 * L.os + 1] * c_hi;
+                    const int nts = dv / 8, groups = (nts + 3) / 4;
+                    for (int unit = warp; unit < H * groups; unit += 8) {
+                        const int h = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = h / rep;
+                        const int r = lane >> 2;
+                        const float c_lo = corr_s[h * QR + r], c_hi = QR == 16 ? corr_s[h * QR + r + 8] : 0.f;
+                        float* op = o_s + ((size_t)h * QR + r) * L.os + nt0 * 8 + (lane & 3) * 2;
+                        float acc[4][4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+                            if (t < n_here) {
+                                acc[t][0] = op[t * 8] * c_lo;
+                                acc[t][1] = op[t * 8 + 1] * c_lo;
+                                if (QR == 16) {
+                                    acc[t][2] = op[8 * L.os + t * 8] * c_hi;
+                                    acc[t][3] = op[8 * L.os + t * 8 + 1] * c_hi;
+                                }
+                            }
                         }
                         const uint32_t a_base = smem_u32(p_s + ((size_t)h * QR + ((lane & 15) & (QR - 1))) * L.ps + (lane >> 4) * 8);
-                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + (lane & 15)) * L.kvs + nt * 8);
+                        const uint32_t b_base = smem_u32(kv_s + ((size_t)kvh * BN + (lane & 15)) * L.kvs + nt0 * 8);
                         for (int kk = 0; kk < BN / 16; ++kk) {
-                            uint32_t af[4], bfr[2];
+                            uint32_t af[4];
                             ldsm_x4(af, a_base + kk * 32);
-                            ldsm_x2_trans(bfr, b_base + (uint32_t)(kk * 16 * L.kvs * 2));
-                            mma_bf16(acc, af, bfr);
+#pragma unroll
+                            for (int t = 0; t < 4; ++t)
+                                if (t < n_here) {
+                                    uint32_t bfr[2];
+                                    ldsm_x2_trans(bfr, b_base + (uint32_t)(kk * 16 * L.kvs * 2) + t * 16);
+                                    mma_bf16(acc[t], af, bfr);
+                                }
                         }
-                        op[0] = acc[0];
-                        op[1] = acc[1];
-                        if (QR == 16) {
-                            op[8 * L.os] = acc[2];
-                            op[8 * L.os + 1] = acc[3];
-                        }
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            if (t < n_here) {
+                                op[t * 8] = acc[t][0];
+                                op[t * 8 + 1] = acc[t][1];
+                                if (QR == 16) {
+                                    op[8 * L.os + t * 8] = acc[t][2];
+                                    op[8 * L.os + t * 8 + 1] = acc[t][3];
+                                }
+                            }
                     }
                 }
                 __syncthreads();

@@ -12,9 +12,8 @@
 
 namespace janis {
 
-constexpr int GLA_KS = 4;          // lanes that share a column of the state (each holds every 4th key channel)
-constexpr int GLA_COLS = 32;       // value columns per CTA
-constexpr int GLA_TT = 16;         // tokens staged per round
+constexpr int GLA_KS = 16;         // lanes that share a column of the state (each holds a run of DPT key channels)
+constexpr int GLA_COLS = 8;        // value columns per CTA
 
 struct GlaRows {
     int row_elems;                 // elements per row of the projected step
@@ -27,19 +26,24 @@ __device__ __forceinline__ float log_sigmoid(float z) {       // -softplus(-z), 
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-// grid (sequences, heads, ceil(dv / GLA_COLS)); 128 threads: thread = (column, ks), ks fastest.
+// grid (sequences, heads, ceil(dv / GLA_COLS)); 128 threads: thread = (column, ks), ks fastest, so that the 16
+// lanes of a column sit in one half of a warp.  Lane ks holds key channels ks * DPT .. ks * DPT + DPT - 1 of its
+// column (DPT a multiple of 4, 16 * DPT >= d; channels beyond d hold zeros and decay 1).  A token's q, k and
+// decays lie in shared memory as runs of DPT floats, each followed by 4 floats of padding, so that the lanes'
+// 16-byte reads fall into different banks.
 template <typename T, int DPT>
 __global__ void __launch_bounds__(GLA_COLS * GLA_KS)
 gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_rows, const T* __restrict__ z_bias,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state,
                 float* __restrict__ o_out) {
-    extern __shared__ float smem[];
+    constexpr int RUN = DPT + 4, TOK = GLA_KS * RUN;       // floats of a lane's run, of a token
+    constexpr int GLA_TT = DPT >= 16 ? 8 : 16;             // tokens staged per round (static shared memory stays under 48 KB)
+    __shared__ __align__(16) float q_s[GLA_TT * TOK];
+    __shared__ __align__(16) float k_s[GLA_TT * TOK];
+    __shared__ __align__(16) float a_s[GLA_TT * TOK];
+    __shared__ float v_s[GLA_TT * GLA_COLS];
     const int d = g.d, dv = g.dv, H = g.H;
-    float* q_s = smem;                       // [TT, d]
-    float* k_s = q_s + GLA_TT * d;           // [TT, d]
-    float* a_s = k_s + GLA_TT * d;           // [TT, d]
-    float* v_s = a_s + GLA_TT * d;           // [TT, GLA_COLS]
     const int seq = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * GLA_COLS;
     const int tid = threadIdx.x, ks = tid % GLA_KS, col = col0 + tid / GLA_KS;
     const bool live = col < dv;
@@ -51,19 +55,26 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_r
     float* st = slot >= 0 ? state + ((size_t)slot * H + h) * d * dv : nullptr;
 #pragma unroll
     for (int ii = 0; ii < DPT; ++ii) {
-        const int i = ks + GLA_KS * ii;
+        const int i = ks * DPT + ii;
         S[ii] = (st != nullptr && live && i < d) ? st[(size_t)i * dv + col] : 0.f;
     }
     for (int t0 = 0; t0 < n_tok; t0 += GLA_TT) {
         const int tt_n = min(GLA_TT, n_tok - t0);
         __syncthreads();
-        for (int u = tid; u < tt_n * d; u += blockDim.x) {
-            const int tt = u / d, c = u % d;
-            const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
-            q_s[u] = to_float(row[g.q_off + h * d + c]) * g.q_scale;
-            k_s[u] = to_float(row[g.k_off + h * d + c]);
-            const float z = to_float(z_rows[(size_t)(row0 + t0 + tt) * H * d + h * d + c]) + to_float(z_bias[h * d + c]);
-            a_s[u] = expf(log_sigmoid(z) * g.inv_tau);
+        for (int u = tid; u < tt_n * GLA_KS * DPT; u += blockDim.x) {
+            const int tt = u / (GLA_KS * DPT), c = u % (GLA_KS * DPT);
+            const int at = tt * TOK + (c / DPT) * RUN + c % DPT;
+            float q = 0.f, k = 0.f, a = 1.f;
+            if (c < d) {
+                const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                q = to_float(row[g.q_off + h * d + c]) * g.q_scale;
+                k = to_float(row[g.k_off + h * d + c]);
+                const float z = to_float(z_rows[(size_t)(row0 + t0 + tt) * H * d + h * d + c]) + to_float(z_bias[h * d + c]);
+                a = expf(log_sigmoid(z) * g.inv_tau);
+            }
+            q_s[at] = q;
+            k_s[at] = k;
+            a_s[at] = a;
         }
         for (int u = tid; u < tt_n * GLA_COLS; u += blockDim.x) {
             const int tt = u / GLA_COLS, c = col0 + u % GLA_COLS;
@@ -72,28 +83,34 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_r
         __syncthreads();
         for (int tt = 0; tt < tt_n; ++tt) {
             const float v = v_s[tt * GLA_COLS + tid / GLA_KS];
-            const float* qq = q_s + tt * d;
-            const float* kk = k_s + tt * d;
-            const float* aa = a_s + tt * d;
+            const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
+            const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
+            const float4* aa = reinterpret_cast<const float4*>(a_s + tt * TOK + ks * RUN);
             float part[4] = {0.f, 0.f, 0.f, 0.f};           // four chains, added in a fixed order
 #pragma unroll
-            for (int ii = 0; ii < DPT; ++ii) {
-                const int i = ks + GLA_KS * ii;
-                if (i < d) {
-                    S[ii] = fmaf(aa[i], S[ii], kk[i] * v);
-                    part[ii & 3] = fmaf(S[ii], qq[i], part[ii & 3]);
-                }
+            for (int i4 = 0; i4 < DPT / 4; ++i4) {
+                const float4 q4 = qq[i4], k4 = kk[i4], a4 = aa[i4];
+                S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * v);
+                S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * v);
+                S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * v);
+                S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * v);
+                part[0] = fmaf(S[4 * i4 + 0], q4.x, part[0]);
+                part[1] = fmaf(S[4 * i4 + 1], q4.y, part[1]);
+                part[2] = fmaf(S[4 * i4 + 2], q4.z, part[2]);
+                part[3] = fmaf(S[4 * i4 + 3], q4.w, part[3]);
             }
             float acc = (part[0] + part[1]) + (part[2] + part[3]);
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
             if (ks == 0 && live) o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = acc;
         }
     }
     if (st != nullptr && live) {
 #pragma unroll
         for (int ii = 0; ii < DPT; ++ii) {
-            const int i = ks + GLA_KS * ii;
+            const int i = ks * DPT + ii;
             if (i < d) st[(size_t)i * dv + col] = S[ii];
         }
     }
@@ -139,22 +156,15 @@ static int gla_scan_launch(const void* rows, const GlaRows& g, const void* z_row
                            const int* seq_first_row, const int* seq_start, const int* seq_end, float* state, float* o_out,
                            int n_seq, cudaStream_t stream) {
     const dim3 grid(n_seq, g.H, (g.dv + GLA_COLS - 1) / GLA_COLS), block(GLA_COLS * GLA_KS);
-    const size_t smem = ((size_t)GLA_TT * (3 * g.d + GLA_COLS)) * sizeof(float);
 #define JANIS_GLA_CASE(DPT)                                                                                            \
-    if (g.d <= GLA_KS * DPT) {                                                                                         \
-        if (smem > 48 * 1024) {                                                                                        \
-            cudaError_t e = cudaFuncSetAttribute(gla_scan_kernel<T, DPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-            if (e != cudaSuccess) return fail("gla_scan: shared memory of %zu bytes refused: %s", smem, cudaGetErrorString(e)); \
-        }                                                                                                              \
-        return launch_kernel("gla_scan", gla_scan_kernel<T, DPT>, grid, block, smem, stream, 1, (const T*)rows, g,     \
-                             (const T*)z_rows, (const T*)z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out); \
-    }
+    if (g.d <= GLA_KS * DPT)                                                                                           \
+        return launch_kernel("gla_scan", gla_scan_kernel<T, DPT>, grid, block, 0, stream, 1, (const T*)rows, g,        \
+                             (const T*)z_rows, (const T*)z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out);
+    JANIS_GLA_CASE(4)
     JANIS_GLA_CASE(8)
     JANIS_GLA_CASE(16)
-    JANIS_GLA_CASE(32)
-    JANIS_GLA_CASE(64)
 #undef JANIS_GLA_CASE
-    return fail("gla_scan: key size %d is above %d", g.d, GLA_KS * 64);
+    return fail("gla_scan: key size %d is above %d", g.d, GLA_KS * 16);
 }
 
 JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off,
