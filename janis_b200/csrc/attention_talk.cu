@@ -273,6 +273,8 @@ struct TalkMmaShape {
     int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
     int bn;             // keys per tile (16, 32, 64)
     int chunk;          // keys per CTA of a decode step whose rows are cut over grid.y CTAs (0: a row's keys in one CTA)
+    int hg;             // groups the heads are cut into: a CTA forms the scores of all heads and the weights and sums of
+                        // its own group (1: all heads in one CTA; more where all heads' sums do not fit shared memory)
     float scale;
 };
 
@@ -281,19 +283,19 @@ struct TalkMmaLayout {
     int qs, kvs, rs, ps, os;       // row strides in elements
 };
 
-__host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, int dv, int qr, int bn) {
+__host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, int dv, int qr, int bn, int hp) {
     TalkMmaLayout L;
     L.qs = d + 8; L.kvs = (d > dv ? d : dv) + 8; L.rs = bn + 4; L.ps = bn + 8; L.os = dv + 4;
     size_t at = 0;
     L.q = at;    at += (size_t)H * qr * L.qs * 2;
     L.kv = at;   at += (size_t)G * bn * L.kvs * 2;
-    L.p = at;    at += (size_t)H * qr * L.ps * 2;
+    L.p = at;    at += (size_t)hp * qr * L.ps * 2;
     at = (at + 15) & ~(size_t)15;
     L.raw = at;  at += (size_t)H * qr * L.rs * 4;
-    L.o = at;    at += (size_t)H * qr * L.os * 4;
-    L.m = at;    at += (size_t)H * qr * 4;
-    L.l = at;    at += (size_t)H * qr * 4;
-    L.corr = at; at += (size_t)H * qr * 4;
+    L.o = at;    at += (size_t)hp * qr * L.os * 4;
+    L.m = at;    at += (size_t)hp * qr * 4;
+    L.l = at;    at += (size_t)hp * qr * 4;
+    L.corr = at; at += (size_t)hp * qr * 4;
     L.talk = at; at += (size_t)H * H * 4;
     L.meta = at; at += (3 * 16 + 64) * 4;
     L.total = at;
@@ -310,7 +312,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                           int n_tok, TalkMmaShape sh) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int H = sh.H, G = sh.G, d = sh.d, dv = sh.dv, QR = sh.qr, BN = sh.bn, rep = H / G;
-    const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, QR, BN);
+    const int HP = H / sh.hg, h0 = ((int)blockIdx.y % sh.hg) * HP;       // this CTA's heads: h0 .. h0 + HP - 1
+    const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, QR, BN, HP);
     bf16* q_s = reinterpret_cast<bf16*>(smem_raw + L.q);
     bf16* kv_s = reinterpret_cast<bf16*>(smem_raw + L.kv);
     bf16* p_s = reinterpret_cast<bf16*>(smem_raw + L.p);
@@ -325,6 +328,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     int* slot_s = pos_s + 32;
     int* base_s = pos_s + 48;                  // where each key of the tile starts in the pools (in rows), -1 beyond the last
     const bool split = sh.chunk > 0;           // the CTA leaves a partial result; the sink joins at the merge
+    const int bn_log2 = BN == 64 ? 6 : (BN == 32 ? 5 : 4);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // the last rows of a prompt see the most keys: they start first
     const int r0 = (int)(gridDim.x - 1 - blockIdx.x) * sh.rows, n_rows = min(sh.rows, n_tok - r0);
@@ -338,20 +342,19 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     }
     if (talk != nullptr)
         for (int u = tid; u < H * H; u += 256) talk_s[u] = talk[u];
-    for (int u = tid; u < H * QR * L.os; u += 256) o_s[u] = 0.f;
-    for (int u = tid; u < H * QR; u += 256) {
+    for (int u = tid; u < HP * QR * L.os; u += 256) o_s[u] = 0.f;
+    for (int u = tid; u < HP * QR; u += 256) {
         m_s[u] = sh.sink && !split ? 0.f : -CUDART_INF_F;
         l_s[u] = sh.sink && !split ? 1.f : 0.f;
     }
     grid_dependency_wait();
-    {   // queries: rows of the step, 16 bytes at a time; rows beyond the step's end are zero
-        const int cpr = d / 8;
-        for (int u = tid; u < H * QR * cpr; u += 256) {
-            const int c8 = u % cpr, r = (u / cpr) % QR, h = u / (cpr * QR);
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (r < n_rows) v = *reinterpret_cast<const uint4*>(q_rows + (size_t)(r0 + r) * q_row_elems + (size_t)h * d + c8 * 8);
-            *reinterpret_cast<uint4*>(q_s + ((size_t)h * QR + r) * L.qs + c8 * 8) = v;
-        }
+    // queries: a warp per (head, row), a lane per 16 bytes; rows beyond the step's end are zero
+    for (int hr = warp; hr < H * QR; hr += 8) {
+        const int h = hr / QR, r = hr & (QR - 1);
+        const bf16* src = q_rows + (size_t)(r0 + (r < n_rows ? r : 0)) * q_row_elems + (size_t)h * d;
+        bf16* dst = q_s + (size_t)hr * L.qs;
+        for (int c8 = lane; c8 < d / 8; c8 += 32)
+            *reinterpret_cast<uint4*>(dst + c8 * 8) = r < n_rows ? *reinterpret_cast<const uint4*>(src + c8 * 8) : make_uint4(0, 0, 0, 0);
     }
     __syncthreads();
     int a = 0;
@@ -362,7 +365,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         if (slot >= 0) {
             int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
             if (split) {
-                first += (int)blockIdx.y * sh.chunk;
+                first += ((int)blockIdx.y / sh.hg) * sh.chunk;
                 last = min(last, first + sh.chunk - 1);
             }
             const int* table = page_table + (size_t)slot * table_stride;
@@ -373,18 +376,17 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     base_s[tid] = j <= last ? (table[j / JANIS_PAGE] * G) * JANIS_PAGE + j % JANIS_PAGE : -1;
                 }
                 __syncthreads();
-                {
-                    const int cpr = d / 8;
-                    for (int u = tid; u < G * BN * cpr; u += 256) {
-                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), at = base_s[jj];
-                        bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
-                        if (at >= 0)
-                            cp_async16(smem_u32(dst), kpool + ((size_t)at + (size_t)g * JANIS_PAGE) * d + c8 * 8);
-                        else
-                            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+                // (a warp per row of the tile, a lane per 16 bytes: no divisions in the addresses)
+                for (int row = warp; row < G * BN; row += 8) {
+                    const int g = row >> bn_log2, jj = row & (BN - 1), at = base_s[jj];
+                    bf16* dst = kv_s + (size_t)row * L.kvs;
+                    const bf16* src = kpool + ((size_t)(at < 0 ? 0 : at) + (size_t)g * JANIS_PAGE) * d;
+                    for (int c8 = lane; c8 < d / 8; c8 += 32) {
+                        if (at >= 0) cp_async16(smem_u32(dst + c8 * 8), src + c8 * 8);
+                        else *reinterpret_cast<uint4*>(dst + c8 * 8) = make_uint4(0, 0, 0, 0);
                     }
-                    cp_async_wait_all();
                 }
+                cp_async_wait_all();
                 __syncthreads();
                 // ---- 1: raw scores of every head; a warp takes a head and up to four tiles of 8 keys, which share
                 //         the queries' fragments and run as four independent chains
@@ -426,18 +428,18 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 __syncthreads();
                 // ---- 2a: the heads' scores mixed, the mask
                 for (int pair = tid; pair < QR * BN; pair += 256) {
-                    const int r = pair / BN, c = pair % BN, j = j0 + c;
+                    const int r = pair >> bn_log2, c = pair & (BN - 1), j = j0 + c;
                     bool seen = r >= a && r < b && j <= pos_s[r];
                     if (seen && sh.block > 0) seen = j >= (pos_s[r] / sh.block) * sh.block;
                     float* at = raw_s + (size_t)r * L.rs + c;
                     const size_t hs = (size_t)QR * L.rs;
                     if (!seen) {
-                        for (int h = 0; h < H; ++h) at[h * hs] = -CUDART_INF_F;
+                        for (int h = h0; h < h0 + HP; ++h) at[h * hs] = -CUDART_INF_F;
                     } else if (talk != nullptr) {
                         float raw[HMAX];
 #pragma unroll
                         for (int g = 0; g < HMAX; ++g) raw[g] = g < H ? at[g * hs] : 0.f;
-                        for (int h = 0; h < H; ++h) {
+                        for (int h = h0; h < h0 + HP; ++h) {
                             const float* tr = talk_s + h * H;
                             float s = 0.f;
 #pragma unroll
@@ -449,8 +451,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- 2b: online softmax of every (head, row); P as bfloat16
-                for (int u = warp; u < H * QR; u += 8) {
-                    const float* src = raw_s + (size_t)u * L.rs;
+                for (int u = warp; u < HP * QR; u += 8) {
+                    const float* src = raw_s + ((size_t)h0 * QR + u) * L.rs;
                     const float s0 = lane < BN ? src[lane] : -CUDART_INF_F;
                     const float s1 = lane + 32 < BN ? src[lane + 32] : -CUDART_INF_F;
                     const float m_old = m_s[u];
@@ -474,25 +476,23 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- values of the tile, into the keys' place
-                {
-                    const int cpr = dv / 8;
-                    for (int u = tid; u < G * BN * cpr; u += 256) {
-                        const int c8 = u % cpr, jj = (u / cpr) % BN, g = u / (cpr * BN), at = base_s[jj];
-                        bf16* dst = kv_s + ((size_t)g * BN + jj) * L.kvs + c8 * 8;
-                        if (at >= 0)
-                            cp_async16(smem_u32(dst), vpool + ((size_t)at + (size_t)g * JANIS_PAGE) * dv + c8 * 8);
-                        else
-                            *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);     // 0 x NaN is NaN
+                for (int row = warp; row < G * BN; row += 8) {
+                    const int g = row >> bn_log2, jj = row & (BN - 1), at = base_s[jj];
+                    bf16* dst = kv_s + (size_t)row * L.kvs;
+                    const bf16* src = vpool + ((size_t)(at < 0 ? 0 : at) + (size_t)g * JANIS_PAGE) * dv;
+                    for (int c8 = lane; c8 < dv / 8; c8 += 32) {
+                        if (at >= 0) cp_async16(smem_u32(dst + c8 * 8), src + c8 * 8);
+                        else *reinterpret_cast<uint4*>(dst + c8 * 8) = make_uint4(0, 0, 0, 0);     // 0 x NaN is NaN
                     }
-                    cp_async_wait_all();
                 }
+                cp_async_wait_all();
                 __syncthreads();
                 // ---- 3: O = O corr + P V; a warp takes a head and up to four tiles of 8 value columns, which share
                 //         P's fragments and run as four independent chains
                 {
                     const int nts = dv / 8, groups = (nts + 3) / 4;
-                    for (int unit = warp; unit < H * groups; unit += 8) {
-                        const int h = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = h / rep;
+                    for (int unit = warp; unit < HP * groups; unit += 8) {
+                        const int h = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = (h0 + h) / rep;
                         const int r = lane >> 2;
                         const float c_lo = corr_s[h * QR + r], c_hi = QR == 16 ? corr_s[h * QR + r + 8] : 0.f;
                         float* op = o_s + ((size_t)h * QR + r) * L.os + nt0 * 8 + (lane & 3) * 2;
@@ -542,8 +542,8 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     __syncthreads();
     if (split) {
         // the chunk's share of row r0: per head the unnormalised sums, then the maximum and the denominator
-        float* dst = partial + ((size_t)r0 * gridDim.y + blockIdx.y) * H * (dv + 2);
-        for (int u = tid; u < H * (dv + 2); u += 256) {
+        float* dst = partial + ((size_t)r0 * (gridDim.y / sh.hg) + blockIdx.y / sh.hg) * H * (dv + 2) + (size_t)h0 * (dv + 2);
+        for (int u = tid; u < HP * (dv + 2); u += 256) {
             const int h = u / (dv + 2), c = u % (dv + 2);
             dst[u] = c < dv ? o_s[(size_t)h * QR * L.os + c] : (c == dv ? m_s[h * QR] : l_s[h * QR]);
         }
@@ -551,9 +551,9 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     }
     // ---- the way out: divide, turn back by the row's position, round
     const int hv = dv >> 1;
-    for (int u = tid; u < n_rows * H * hv; u += 256) {
-        const int m = u % hv, h = (u / hv) % H, r = u / (hv * H);
-        bf16* o_row = out + (size_t)(r0 + r) * H * dv + (size_t)h * dv;
+    for (int u = tid; u < n_rows * HP * hv; u += 256) {
+        const int m = u % hv, h = (u / hv) % HP, r = u / (hv * HP);
+        bf16* o_row = out + (size_t)(r0 + r) * H * dv + (size_t)(h0 + h) * dv;
         float lo = 0.f, hi = 0.f;
         if (slot_s[r] >= 0) {
             const float inv_l = 1.f / l_s[h * QR + r];
@@ -662,14 +662,17 @@ static TalkMmaShape talk_mma_shape(int H, int G, int d, int dv, int one_row, siz
     TalkMmaShape sh = {};
     if (H > 32 || d % 16 || dv % 8 || (dv & 1)) return sh;
     static const int order[6][2] = {{16, 64}, {16, 32}, {8, 64}, {8, 32}, {16, 16}, {8, 16}};
-    for (int i = 0; i < 6; ++i) {
-        const int qr = order[i][0], bn = order[i][1];
-        if (one_row && qr != 8) continue;
-        const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, qr, bn);
-        if (L.total <= 220 * 1024) {
-            sh.qr = qr; sh.bn = bn; sh.rows = one_row ? 1 : qr;
-            *bytes = L.total;
-            return sh;
+    for (int hg = 1; hg <= 8; hg *= 2) {            // all heads' sums in one CTA where they fit, else the heads in groups
+        if (H % hg) break;
+        for (int i = 0; i < 6; ++i) {
+            const int qr = order[i][0], bn = order[i][1];
+            if (one_row && qr != 8) continue;
+            const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, qr, bn, H / hg);
+            if (L.total <= 220 * 1024) {
+                sh.qr = qr; sh.bn = bn; sh.rows = one_row ? 1 : qr; sh.hg = hg;
+                *bytes = L.total;
+                return sh;
+            }
         }
     }
     return sh;
@@ -686,7 +689,7 @@ static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_p
         if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
         most = bytes;
     }
-    const dim3 grid((T + sh.rows - 1) / sh.rows, sh.chunk > 0 ? n_chunks : 1), block(256);
+    const dim3 grid((T + sh.rows - 1) / sh.rows, (sh.chunk > 0 ? n_chunks : 1) * sh.hg), block(256);
     if (launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
                       q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
                       table_stride, talk, inv_v, (bf16*)out, partial, T, sh))

@@ -26,14 +26,24 @@ __device__ __forceinline__ float log_sigmoid(float z) {       // -softplus(-z), 
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
+// a[t, c] = sigmoid(z[t, c] + b[c])^(1/tau) as floats, once per step (every column group of a head reads them)
+template <typename T>
+__global__ void __launch_bounds__(256)
+gla_decay_kernel(const T* __restrict__ z, const T* __restrict__ bias, float* __restrict__ a, size_t n, int width, float inv_tau) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        a[i] = expf(log_sigmoid(to_float(z[i]) + to_float(bias[i % width])) * inv_tau);
+}
+
 // grid (sequences, heads, ceil(dv / GLA_COLS)); 128 threads: thread = (column, ks), ks fastest, so that the 16
-// lanes of a column sit in one half of a warp.  Lane ks holds key channels ks * DPT .. ks * DPT + DPT - 1 of its
+// lanes of a column sit in one half of a warp (tiles of 16 tokens, or of 8 at the largest key sizes).  Lane ks holds key channels ks * DPT .. ks * DPT + DPT - 1 of its
 // column (DPT a multiple of 4, 16 * DPT >= d; channels beyond d hold zeros and decay 1).  A token's q, k and
 // decays lie in shared memory as runs of DPT floats, each followed by 4 floats of padding, so that the lanes'
 // 16-byte reads fall into different banks.
 template <typename T, int DPT>
 __global__ void __launch_bounds__(GLA_COLS * GLA_KS)
-gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_rows, const T* __restrict__ z_bias,
+gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__ decay,
                 const int* __restrict__ seq_slot, const int* __restrict__ seq_first_row,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_end, float* __restrict__ state,
                 float* __restrict__ o_out) {
@@ -58,30 +68,50 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_r
         const int i = ks * DPT + ii;
         S[ii] = (st != nullptr && live && i < d) ? st[(size_t)i * dv + col] : 0.f;
     }
+    // A tile's q, k and decays travel through registers: a fixed number of elements a thread, all of their loads
+    // asked for at once, and those of the next tile while this one is computed.  Tokens beyond the sequence's end
+    // become q = k = v = 0 and decay 1, which change nothing, so a tile always runs all of its tokens.
+    constexpr int PER = GLA_TT * GLA_KS * DPT / (GLA_COLS * GLA_KS);
+    float qv[PER], kv[PER], av[PER], vv = 0.f;
+    auto fetch = [&](int t0) {
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int u = tid + e * (GLA_COLS * GLA_KS);
+            const int tt = u / (GLA_KS * DPT), c = u % (GLA_KS * DPT);
+            qv[e] = kv[e] = 0.f;
+            av[e] = 1.f;
+            if (t0 + tt < n_tok && c < d) {
+                const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                qv[e] = to_float(row[g.q_off + h * d + c]);
+                kv[e] = to_float(row[g.k_off + h * d + c]);
+                av[e] = decay[(size_t)(row0 + t0 + tt) * H * d + h * d + c];
+            }
+        }
+        vv = 0.f;
+        if (tid < GLA_TT * GLA_COLS) {
+            const int tt = tid / GLA_COLS, c = col0 + tid % GLA_COLS;
+            if (t0 + tt < n_tok && c < dv) vv = to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.v_off + h * dv + c]);
+        }
+    };
+    fetch(0);
     for (int t0 = 0; t0 < n_tok; t0 += GLA_TT) {
-        const int tt_n = min(GLA_TT, n_tok - t0);
-        __syncthreads();
-        for (int u = tid; u < tt_n * GLA_KS * DPT; u += blockDim.x) {
+        __syncthreads();                       // the tile before has been read
+#pragma unroll
+        for (int e = 0; e < PER; ++e) {
+            const int u = tid + e * (GLA_COLS * GLA_KS);
             const int tt = u / (GLA_KS * DPT), c = u % (GLA_KS * DPT);
             const int at = tt * TOK + (c / DPT) * RUN + c % DPT;
-            float q = 0.f, k = 0.f, a = 1.f;
-            if (c < d) {
-                const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
-                q = to_float(row[g.q_off + h * d + c]) * g.q_scale;
-                k = to_float(row[g.k_off + h * d + c]);
-                const float z = to_float(z_rows[(size_t)(row0 + t0 + tt) * H * d + h * d + c]) + to_float(z_bias[h * d + c]);
-                a = expf(log_sigmoid(z) * g.inv_tau);
-            }
-            q_s[at] = q;
-            k_s[at] = k;
-            a_s[at] = a;
+            q_s[at] = qv[e] * g.q_scale;
+            k_s[at] = kv[e];
+            a_s[at] = av[e];
         }
-        for (int u = tid; u < tt_n * GLA_COLS; u += blockDim.x) {
-            const int tt = u / GLA_COLS, c = col0 + u % GLA_COLS;
-            v_s[u] = c < dv ? to_float(rows[(size_t)(row0 + t0 + tt) * g.row_elems + g.v_off + h * dv + c]) : 0.f;
-        }
+        if (tid < GLA_TT * GLA_COLS) v_s[tid] = vv;
         __syncthreads();
-        for (int tt = 0; tt < tt_n; ++tt) {
+        if (t0 + GLA_TT < n_tok) fetch(t0 + GLA_TT);
+        // the tile's tokens in order; each lane's share of o_t stays in a register until the tile is done
+        float part_o[GLA_TT];
+#pragma unroll
+        for (int tt = 0; tt < GLA_TT; ++tt) {
             const float v = v_s[tt * GLA_COLS + tid / GLA_KS];
             const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
             const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
@@ -99,13 +129,32 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const T* __restrict__ z_r
                 part[2] = fmaf(S[4 * i4 + 2], q4.z, part[2]);
                 part[3] = fmaf(S[4 * i4 + 3], q4.w, part[3]);
             }
-            float acc = (part[0] + part[1]) + (part[2] + part[3]);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            if (ks == 0 && live) o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = acc;
+            part_o[tt] = (part[0] + part[1]) + (part[2] + part[3]);
         }
+        // the 16 lanes of a column add their shares of all the tile's tokens at once: every stage halves the tokens
+        // a lane still carries (the lanes whose bit is set keep the upper half), so 15 shuffles do what 64 would
+        int n = GLA_TT;
+#pragma unroll
+        for (int off = GLA_KS / 2; off >= 1; off >>= 1) {
+            const bool upper = (ks & off) != 0;
+            if (n > 1) {
+                const int half = n / 2;
+#pragma unroll
+                for (int i = 0; i < GLA_TT / 2; ++i)
+                    if (i < half) {
+                        const float mine = upper ? part_o[i + half] : part_o[i];
+                        const float theirs = upper ? part_o[i] : part_o[i + half];
+                        part_o[i] = mine + __shfl_xor_sync(0xffffffffu, theirs, off);
+                    }
+                n = half;
+            } else {
+                part_o[0] += __shfl_xor_sync(0xffffffffu, part_o[0], off);
+            }
+        }
+        // lane ks now holds token ks * GLA_TT / 16 of the tile (lanes that share a token hold the same sum)
+        constexpr int SHARE = GLA_KS / GLA_TT;              // 1, or 2 with tiles of 8 tokens
+        const int tt = ks / SHARE;
+        if (live && ks % SHARE == 0 && t0 + tt < n_tok) o_out[(size_t)(row0 + t0 + tt) * H * dv + h * dv + col] = part_o[0];
     }
     if (st != nullptr && live) {
 #pragma unroll
@@ -152,14 +201,14 @@ JANIS_EXPORT void janis_mixers_set_overlap(int on) { overlap_launches() = on ? 1
 JANIS_EXPORT const char* janis_last_error() { return error_buffer(); }
 
 template <typename T>
-static int gla_scan_launch(const void* rows, const GlaRows& g, const void* z_rows, const void* z_bias, const int* seq_slot,
+static int gla_scan_launch(const void* rows, const GlaRows& g, const float* decay, const int* seq_slot,
                            const int* seq_first_row, const int* seq_start, const int* seq_end, float* state, float* o_out,
                            int n_seq, cudaStream_t stream) {
     const dim3 grid(n_seq, g.H, (g.dv + GLA_COLS - 1) / GLA_COLS), block(GLA_COLS * GLA_KS);
 #define JANIS_GLA_CASE(DPT)                                                                                            \
     if (g.d <= GLA_KS * DPT)                                                                                           \
         return launch_kernel("gla_scan", gla_scan_kernel<T, DPT>, grid, block, 0, stream, 1, (const T*)rows, g,        \
-                             (const T*)z_rows, (const T*)z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out);
+                             decay, seq_slot, seq_first_row, seq_start, seq_end, state, o_out);
     JANIS_GLA_CASE(4)
     JANIS_GLA_CASE(8)
     JANIS_GLA_CASE(16)
@@ -168,20 +217,30 @@ static int gla_scan_launch(const void* rows, const GlaRows& g, const void* z_row
 }
 
 JANIS_EXPORT int janis_gla_scan(const void* rows, int dtype, int row_elems, int q_off, int k_off, int v_off,
-                                const void* z_rows, const void* z_bias, const int* seq_slot, const int* seq_first_row,
-                                const int* seq_start, const int* seq_end, float* state, float* o_out, int n_seq, int H,
-                                int d, int dv, float q_scale, float tau, cudaStream_t stream) {
-    if (n_seq <= 0) return 0;
+                                const void* z_rows, const void* z_bias, float* decay, int n_tok, const int* seq_slot,
+                                const int* seq_first_row, const int* seq_start, const int* seq_end, float* state,
+                                float* o_out, int n_seq, int H, int d, int dv, float q_scale, float tau, cudaStream_t stream) {
+    if (n_seq <= 0 || n_tok <= 0) return 0;
     if (H <= 0 || d <= 0 || dv <= 0) return fail("gla_scan: sizes %d heads, %d x %d", H, d, dv);
     if (!(tau > 0.f)) return fail("gla_scan: tau must be positive");
     if (H > 65535) return fail("gla_scan: too many heads (%d)", H);
     GlaRows g;
     g.row_elems = row_elems; g.q_off = q_off; g.k_off = k_off; g.v_off = v_off;
     g.H = H; g.d = d; g.dv = dv; g.q_scale = q_scale; g.inv_tau = 1.0f / tau;
-    if (dtype == JANIS_F32)
-        return gla_scan_launch<float>(rows, g, z_rows, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
-    if (dtype == JANIS_BF16)
-        return gla_scan_launch<bf16>(rows, g, z_rows, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+    const size_t n = (size_t)n_tok * H * d, want = (n + 255) / 256;
+    const dim3 dgrid((unsigned)(want < 148 * 16 ? want : 148 * 16)), dblock(256);
+    if (dtype == JANIS_F32) {
+        if (launch_kernel("gla_decay", gla_decay_kernel<float>, dgrid, dblock, 0, stream, 1, (const float*)z_rows,
+                          (const float*)z_bias, decay, n, H * d, g.inv_tau))
+            return 1;
+        return gla_scan_launch<float>(rows, g, decay, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+    }
+    if (dtype == JANIS_BF16) {
+        if (launch_kernel("gla_decay", gla_decay_kernel<bf16>, dgrid, dblock, 0, stream, 1, (const bf16*)z_rows,
+                          (const bf16*)z_bias, decay, n, H * d, g.inv_tau))
+            return 1;
+        return gla_scan_launch<bf16>(rows, g, decay, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, stream);
+    }
     return fail("gla_scan: unknown dtype %d", dtype);
 }
 

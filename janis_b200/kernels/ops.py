@@ -140,7 +140,7 @@ def mixers():
         lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
-        lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, I, F, F, P]
+        lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
         lib.janis_mixers_set_overlap.restype = None
@@ -820,13 +820,17 @@ def talk_attention_set_kernel(which: int = 1) -> None:
 
 
 def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state,
-             o_out, n_seq: int, H: int, d: int, dv: int, q_scale: float, tau: float):
+             o_out, n_seq: int, H: int, d: int, dv: int, q_scale: float, tau: float, decay=None):
     """The recurrence of gated linear attention over the tokens each sequence brings to the step, in order:
     a = sigmoid(z + z_bias)^(1/tau) per key channel, S = diag(a) S + k v^T, o = S^T (q q_scale).
     rows [T, width] holds the projections (q [H, d] at q_off, k at k_off, v [H, dv] at v_off), z [T, H d] the
     projected decay logits; state float32 [slots, H, d, dv] is read and written back for sequences whose slot is
-    >= 0; o_out float32 [T, H dv]."""
+    >= 0; o_out float32 [T, H dv]; decay float32 [T, H d] receives the decays (a kernel of its own forms them once
+    for all the CTAs of a head; allocated here when not given)."""
     T, width = rows.shape
+    if decay is None:
+        decay = torch.empty((T, H * d), dtype=torch.float32, device=rows.device)
+    _t(decay, "decay", torch.float32, (T, H * d))
     _t(rows, "rows", _FLOATS, (T, None))
     _t(z, "z", rows.dtype, (T, H * d))
     _t(z_bias, "z_bias", rows.dtype, (H * d,))
@@ -838,9 +842,9 @@ def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_
             raise KernelError(f"gla_scan: {name} shorter than the step's sequences")
     lib = mixers()
     _check(lib, lib.janis_gla_scan(rows.data_ptr(), _DT[rows.dtype], width, q_off, k_off, v_off, z.data_ptr(),
-                                   z_bias.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(), seq_start.data_ptr(),
-                                   seq_end.data_ptr(), state.data_ptr(), o_out.data_ptr(), n_seq, H, d, dv,
-                                   float(q_scale), float(tau), _stream()))
+                                   z_bias.data_ptr(), decay.data_ptr(), T, seq_slot.data_ptr(), seq_first_row.data_ptr(),
+                                   seq_start.data_ptr(), seq_end.data_ptr(), state.data_ptr(), o_out.data_ptr(), n_seq,
+                                   H, d, dv, float(q_scale), float(tau), _stream()), kernels=2)
     return o_out
 
 

@@ -86,7 +86,8 @@ class GatedLinearAttention(Mixer):
                       ws.buf("gla.z", (T, H * d), rt.dtype))
         o = ws.buf("gla.o", (T, H * dv), torch.float32)
         ops.gla_scan(rows, q_off, k_off, v_off, z, self.b_a2, ctx.seq_slot, ctx.seq_first_row, ctx.seq_start,
-                     ctx.seq_end, st.data, o, ctx.n_seq, H, d, dv, self.q_scale, self.tau)
+                     ctx.seq_end, st.data, o, ctx.n_seq, H, d, dv, self.q_scale, self.tau,
+                     decay=ws.buf("gla.decay", (T, H * d), torch.float32))
         y = ws.buf("gla.y", (T, H * dv), rt.dtype)
         ops.head_norm_gate(o, rows, g_off, self.w_norm, self.norm_eps, y, H, dv)
         return rt.linear(y, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

@@ -378,7 +378,7 @@ def talk_attention_scratch_floats(T, n_chunks, H, dv):
 
 
 def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_start, seq_end, state, o_out, n_seq, H,
-             d, dv, q_scale, tau):
+             d, dv, q_scale, tau, decay=None):
     for s in range(n_seq):
         slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
         if n <= 0:
