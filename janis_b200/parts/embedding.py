@@ -51,8 +51,6 @@ class LMHead(Part):
         return {self.table_name: TensorSpec((self.vocab, self.hidden), init_std=self.init_std)}
 
     def load(self, store, rt: Runtime):
-        if rt.dtype == torch.bfloat16 and self.hidden % 8:
-            raise ValueError(f"the bfloat16 products need a hidden width that is a multiple of 8, found {self.hidden}")
         self.table = store.get(self.table_name, rt.dtype).contiguous()
 
     def forward(self, y, ctx: StepContext, out):
@@ -61,9 +59,10 @@ class LMHead(Part):
         R = y.shape[0]
         if ctx.rt.dtype == torch.float32:
             return ops.gemm_f32(y, self.table, out, self.softcap)
-        if R <= ops.GEMV_FAST_ROWS:
+        vec = self.hidden % 8 == 0        # the skinny products read 16 bytes at a time; other widths take the library's
+        if R <= ops.GEMV_FAST_ROWS and vec:
             return ops.gemv_bf16(y, self.table, out, ops.EPI_SOFTCAP, self.softcap)
-        if R <= ops.TC05_MAX_ROWS:
+        if R <= ops.TC05_MAX_ROWS and vec:
             return ops.gemm_tc05(y, self.table, out, ops.EPI_SOFTCAP, self.softcap)   # float32 logits straight from tensor memory
         # many rows: the library's product with float32 output, then the cap
         ops.matmul_bf16_to_f32(y, self.table, out)

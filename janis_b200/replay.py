@@ -85,13 +85,15 @@ def main(argv=None) -> int:
                     help="bfloat16: the kernels and precisions of serving; float32: everything in true 32-bit")
     ap.add_argument("--out", required=True, help="folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens that live requests hold at any time (each rounded up to 64); sizes the cache")
+                    help="most tokens that live requests hold at any time; sizes the cache (with room to spare for partly filled pages)")
     ap.add_argument("--no-graphs", action="store_true", help="launch decode steps kernel by kernel")
     args = ap.parse_args(argv)
     from .engine import engine as eng_mod
     from .config.base import read_config_json
     raw = read_config_json(args.model)
-    max_tokens = max(64, args.max_tokens)
+    # the cache hands out whole pages of 64 tokens and as many slots as pages: room for 256 requests that each hold
+    # a partly filled page on top of the tokens asked for
+    max_tokens = max(64, args.max_tokens) + 64 * 256
     ctx = max(int(raw.get("max_position_embeddings", 0) or 0), (max_tokens + 63) // 64 * 64)
     engine = eng_mod.open(args.model, dtype=args.dtype, max_tokens=max_tokens, max_context=ctx,
                           use_graphs=not args.no_graphs)

