@@ -259,10 +259,7 @@ bias_act_kernel(T* __restrict__ x, const T* __restrict__ bias, size_t n, int N, 
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         float z = to_float(x[i]);
         if (bias != nullptr) z += to_float(bias[i % N]);
-        if (act == 1) z = z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
-        else if (act == 2) z = gelu_tanh(z);
-        else if (act == 3) z = z / (1.0f + expf(-z));
-        x[i] = from_float<T>(z);
+        x[i] = from_float<T>(dense_act(z, act, a_pos, a_neg));
     }
 }
 
@@ -282,11 +279,7 @@ bias_act_vec_kernel(T* __restrict__ x, const T* __restrict__ bias, size_t n_vec,
             for (int e = 0; e < VEC; ++e) z[e] += b[e];
         }
 #pragma unroll
-        for (int e = 0; e < VEC; ++e) {
-            if (act == 1) z[e] = z[e] > 0.f ? fmaf(a_pos * z[e], z[e], 0.5f * z[e]) : fmaf(a_neg, expm1f(z[e]) - z[e], 0.5f * z[e]);
-            else if (act == 2) z[e] = gelu_tanh(z[e]);
-            else if (act == 3) z[e] = z[e] / (1.0f + expf(-z[e]));
-        }
+        for (int e = 0; e < VEC; ++e) z[e] = dense_act(z[e], act, a_pos, a_neg);
         Vec16<T>::store(x + i * VEC, z);
     }
 }

@@ -86,7 +86,7 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {   // read once: do 
 template <int MT, int U, int CL, int NW, typename TO, bool ROPE = false>
 __global__ void __launch_bounds__(NW * 32)
 gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __restrict__ out, int M, int N,
-                 int K, int epi, float cap, const RopeStore rs) {
+                 int K, int epi, float cap, const RopeStore rs, const BiasAct ba) {
     __shared__ float red[NW][MT][32][4];
     __shared__ __align__(16) float cta_sum[MT * 128];        // this CTA's sum over its warps; read by CTA 0 of the cluster
     constexpr bool PUSH = JANIS_GEMV_PUSH && CL > 1 && MT <= 4;      // (the gather area of 8 row tiles does not fit)
@@ -357,6 +357,11 @@ gemv_bf16_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, TO* __r
         const int n = r0 + (ln >> 2) + (c >> 1) * 8;
         if (m < M && n < N) {
             if (epi == EPI_SOFTCAP && cap > 0.f) v = cap * tanhf(v / cap);
+            if (ba.bias != nullptr || ba.act != 0) {      // round as the product alone would, then bias and activation
+                v = __bfloat162float(__float2bfloat16_rn(v));
+                if (ba.bias != nullptr) v += __bfloat162float(ba.bias[n]);
+                v = dense_act(v, ba.act, ba.a_pos, ba.a_neg);
+            }
             out[(size_t)m * N + n] = from_float<TO>(v);
         }
     }
@@ -372,27 +377,27 @@ JANIS_EXPORT void janis_gemv_small_ctas(int on) { g_gemv_small_ctas = on ? 1 : 0
 
 template <int MT, int U, int CL, typename TO, bool ROPE = false>
 static int launch_one(const bf16* x, const bf16* W, TO* out, int M, int N, int K, int epi, float cap,
-                      const RopeStore& rs, cudaStream_t stream) {
+                      const RopeStore& rs, cudaStream_t stream, const BiasAct ba = BiasAct{nullptr, 0, 0.f, 0.f}) {
     const int tiles = (N + 15) / 16;
     if (CL == 1) {
         // many tiles: CTAs of 4 warps, so that more of them are resident and the last wave is short
         if (tiles >= 1024 && g_gemv_small_ctas && !ROPE)
             return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, 4, TO, false>, dim3(tiles), dim3(4 * 32), 0, stream, 1,
-                                 x, W, out, M, N, K, epi, cap, rs);
+                                 x, W, out, M, N, K, epi, cap, rs, ba);
         return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, 1, GEMV_WARPS, TO, ROPE>, dim3(tiles), dim3(GEMV_WARPS * 32), 0,
-                             stream, 1, x, W, out, M, N, K, epi, cap, rs);
+                             stream, 1, x, W, out, M, N, K, epi, cap, rs, ba);
     }
     return launch_kernel("gemv_bf16", gemv_bf16_kernel<MT, U, CL, GEMV_WARPS, TO, ROPE>, dim3(tiles * CL), dim3(GEMV_WARPS * 32),
-                         0, stream, CL, x, W, out, M, N, K, epi, cap, rs);
+                         0, stream, CL, x, W, out, M, N, K, epi, cap, rs, ba);
 }
 
 template <int MT, int U>
 static int launch_gemv(const bf16* x, const bf16* W, void* out, int out_dtype, int M, int N, int K, int epi,
-                       float cap, int cluster, cudaStream_t stream) {
+                       float cap, int cluster, cudaStream_t stream, const BiasAct ba = BiasAct{nullptr, 0, 0.f, 0.f}) {
     const RopeStore none = {};
 #define JANIS_GEMV(CL)                                                                                                \
-    (out_dtype == JANIS_BF16 ? launch_one<MT, U, CL, bf16>(x, W, (bf16*)out, M, N, K, epi, cap, none, stream)          \
-                             : launch_one<MT, U, CL, float>(x, W, (float*)out, M, N, K, epi, cap, none, stream))
+    (out_dtype == JANIS_BF16 ? launch_one<MT, U, CL, bf16>(x, W, (bf16*)out, M, N, K, epi, cap, none, stream, ba)      \
+                             : launch_one<MT, U, CL, float>(x, W, (float*)out, M, N, K, epi, cap, none, stream, ba))
     if (cluster >= 4) return JANIS_GEMV(4);
     if (cluster >= 2) return JANIS_GEMV(2);
     return JANIS_GEMV(1);
@@ -438,6 +443,25 @@ JANIS_EXPORT int janis_gemv_bf16(const void* x, const void* W, void* out, int ou
     if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
     return launch_gemv<8, 1>(xp, wp, out, out_dtype, M, N, K, epi, cap, cluster, stream);
+}
+
+// The same product with a bias (may be null) and an activation of a dense feed-forward (the codes of bias_act) in its
+// epilogue: bit for bit what gemv_bf16 into bfloat16 followed by bias_act leaves.
+JANIS_EXPORT int janis_gemv_bf16_bias_act(const void* x, const void* W, void* out, int M, int N, int K, const void* bias,
+                                          int act, float a_pos, float a_neg, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64) return fail("gemv_bf16_bias_act: at most 64 rows, found %d", M);
+    if (K <= 0 || K % 8) return fail("gemv_bf16_bias_act: K must be a positive multiple of 8, found %d", K);
+    if (act < 0 || act > 3) return fail("gemv_bf16_bias_act: unknown activation %d", act);
+    if (((uintptr_t)x | (uintptr_t)W) & 15) return fail("gemv_bf16_bias_act: operands must be 16-byte aligned");
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    const BiasAct ba = {(const bf16*)bias, act, a_pos, a_neg};
+    const int cluster = choose_cluster((N + 15) / 16, (K + 31) / 32);
+    if (M <= 8) return launch_gemv<1, JANIS_GEMV_U1>(xp, wp, out, JANIS_BF16, M, N, K, EPI_NONE, 0.f, cluster, stream, ba);
+    if (M <= 16) return launch_gemv<2, 4>(xp, wp, out, JANIS_BF16, M, N, K, EPI_NONE, 0.f, cluster, stream, ba);
+    if (M <= 32) return launch_gemv<4, 2>(xp, wp, out, JANIS_BF16, M, N, K, EPI_NONE, 0.f, cluster, stream, ba);
+    return launch_gemv<8, 1>(xp, wp, out, JANIS_BF16, M, N, K, EPI_NONE, 0.f, cluster, stream, ba);
 }
 
 // The q/k/v projection of a decode step with the rotary encoding and the cache write in its epilogue (bfloat16,

@@ -60,6 +60,7 @@ def core():
         lib.janis_kv_store.argtypes = [P, I, P, P, P, P, I, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_f32.argtypes = [P, P, P, I, I, I, F, P]
         lib.janis_gemv_bf16.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
+        lib.janis_gemv_bf16_bias_act.argtypes = [P, P, P, I, I, I, P, I, F, F, P]
         lib.janis_gemv_rope_store.argtypes = [P, P, P, I, I, P, P, P, P, P, I, I, I, I, P, P, P, I, I, P]
         lib.janis_gemm_tc05.argtypes = [P, P, P, I, I, I, I, I, F, I, P]
         lib.janis_tc05_timeouts.restype = I
@@ -382,6 +383,19 @@ def gemv_bf16(x, w, out, epilogue: int = EPI_NONE, cap: float = 0.0, cluster: in
     _check(lib, lib.janis_gemv_bf16(_t(x, "x", torch.bfloat16, (M, K)), _t(w, "w", torch.bfloat16, (N, K)),
                                     _t(out, "out", _FLOATS, (M, n_out)), _DT[out.dtype], M, N, K, epilogue,
                                     float(cap), int(cluster), _stream()))
+    return out
+
+
+def gemv_bf16_bias_act(x, w, out, bias, act: int = 0, a_pos: float = 0.0, a_neg: float = 0.0):
+    """out = act(bf16(x w^T) + bias) for up to 64 rows in one kernel: the bits that `gemv_bf16` into bfloat16 followed
+    by `bias_act` leaves (bias [N] bfloat16 or None; act and its two numbers as in `bias_act`)."""
+    M, K = x.shape
+    N = w.shape[0]
+    lib = core()
+    _check(lib, lib.janis_gemv_bf16_bias_act(_t(x, "x", torch.bfloat16, (M, K)), _t(w, "w", torch.bfloat16, (N, K)),
+                                             _t(out, "out", torch.bfloat16, (M, N)), M, N, K,
+                                             _t(bias, "bias", torch.bfloat16, (N,)) if bias is not None else None,
+                                             int(act), float(a_pos), float(a_neg), _stream()))
     return out
 
 

@@ -133,10 +133,15 @@ class DenseMLP(FeedForward):
         rt, ws, ops = ctx.rt, ctx.ws, ctx.rt.ops
         T = ctx.n_tok
         a = ws.buf("ffn.act", (T, self.intermediate), rt.dtype)
-        rt.linear(x, self.w_up, a)
-        kind = {"xielu": ops.ACT_XIELU, "gelu_tanh": ops.ACT_GELU, "silu": ops.ACT_SILU_PLAIN}[self.act]
-        ops.bias_act(a, self.b_up, kind, self.a_pos, self.a_neg)
         out = ws.buf("ffn.out", (T, self.hidden), rt.dtype)
+        kind = {"xielu": ops.ACT_XIELU, "gelu_tanh": ops.ACT_GELU, "silu": ops.ACT_SILU_PLAIN}[self.act]
+        if (rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS and self.hidden % 8 == 0 and self.intermediate % 8 == 0
+                and hasattr(ops, "gemv_bf16_bias_act")):
+            # few rows: bias and activation in the epilogue of the skinny products (the same bits as the two kernels)
+            ops.gemv_bf16_bias_act(x, self.w_up, a, self.b_up, kind, self.a_pos, self.a_neg)
+            return ops.gemv_bf16_bias_act(a, self.w_down, out, self.b_down, ops.ACT_NONE)
+        rt.linear(x, self.w_up, a)
+        ops.bias_act(a, self.b_up, kind, self.a_pos, self.a_neg)
         rt.linear(a, self.w_down, out)
         if self.b_down is not None:
             ops.bias_act(out, self.b_down, ops.ACT_NONE)

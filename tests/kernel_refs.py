@@ -313,6 +313,11 @@ def bias_act(x, bias, act=ACT_NONE, a_pos=0.0, a_neg=0.0):
     return x
 
 
+def gemv_bf16_bias_act(x, w, out, bias, act=ACT_NONE, a_pos=0.0, a_neg=0.0):
+    out.copy_((x.double() @ w.double().T).to(out.dtype))
+    return bias_act(out, bias, act, a_pos, a_neg)
+
+
 def _turn(x, pos, inv, sign=1.0):
     """x [..., n] rotated by sign * pos * inv over pairs (i, i + len(inv)); angles float32 as the kernels form them."""
     h = inv.numel()

@@ -374,6 +374,23 @@ def test_bias_and_activation_kernel_against_its_statement(dtype):
         assert (got.cpu().double() - want.double()).abs().max().item() <= tol * max(1.0, want.double().abs().max().item())
 
 
+@GPU
+def test_bias_and_activation_in_the_product_are_the_two_kernels_bit_for_bit():
+    from janis_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    for M, N, K in ((1, 72, 64), (8, 384, 256), (13, 200, 96), (16, 2304, 1024)):
+        x = torch.randn(M, K, generator=g).bfloat16().cuda()
+        w = (torch.randn(N, K, generator=g) * K ** -0.5).bfloat16().cuda()
+        b = torch.randn(N, generator=g).bfloat16().cuda()
+        for act, bias in ((ops.ACT_XIELU, b), (ops.ACT_NONE, b), (ops.ACT_GELU, None)):
+            two = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            ops.gemv_bf16(x, w, two)
+            ops.bias_act(two, bias, act, 0.8, 0.6)
+            one = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            ops.gemv_bf16_bias_act(x, w, one, bias, act, 0.8, 0.6)
+            assert torch.equal(one, two), (M, N, K, act)
+
+
 # ---------------------------------------------------------------------------
 # the engine against the plain model
 # ---------------------------------------------------------------------------
