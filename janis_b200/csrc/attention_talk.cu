@@ -233,7 +233,7 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
 // ---------------------------------------------------------------------------
 // The tensor-core kernel (bfloat16, d a multiple of 16, dv a multiple of 8, up to 32 heads).
 //
-// A CTA of 8 warps owns up to QR (16 or 8) consecutive rows of the packed step, all heads together, since every
+// A CTA of 16 warps owns up to QR (16 or 8) consecutive rows of the packed step, all heads together, since every
 // head's weights need every head's scores.  Rows of one sequence form a run; a run's keys (from the first row's
 // block start to the last row's position) come in tiles of BN keys.  Per tile, three phases with the scores
 // passing through shared memory as floats:
@@ -266,6 +266,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+
+constexpr int TALK_MMA_WARPS = 16, TALK_MMA_THREADS = TALK_MMA_WARPS * 32;
 
 struct TalkMmaShape {
     int H, G, d, dv, block, sink;
@@ -303,7 +305,7 @@ __host__ __device__ inline TalkMmaLayout talk_mma_layout(int H, int G, int d, in
 }
 
 template <int HMAX>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(TALK_MMA_THREADS)
 talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, const int* __restrict__ tok_pos,
                           const int* __restrict__ tok_seq, const int* __restrict__ seq_slot,
                           const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
@@ -341,15 +343,15 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         slot_s[tid] = in ? seq_slot[sq] : -1;
     }
     if (talk != nullptr)
-        for (int u = tid; u < H * H; u += 256) talk_s[u] = talk[u];
-    for (int u = tid; u < HP * QR * L.os; u += 256) o_s[u] = 0.f;
-    for (int u = tid; u < HP * QR; u += 256) {
+        for (int u = tid; u < H * H; u += TALK_MMA_THREADS) talk_s[u] = talk[u];
+    for (int u = tid; u < HP * QR * L.os; u += TALK_MMA_THREADS) o_s[u] = 0.f;
+    for (int u = tid; u < HP * QR; u += TALK_MMA_THREADS) {
         m_s[u] = sh.sink && !split ? 0.f : -CUDART_INF_F;
         l_s[u] = sh.sink && !split ? 1.f : 0.f;
     }
     grid_dependency_wait();
     // queries: a warp per (head, row), a lane per 16 bytes; rows beyond the step's end are zero
-    for (int hr = warp; hr < H * QR; hr += 8) {
+    for (int hr = warp; hr < H * QR; hr += TALK_MMA_WARPS) {
         const int h = hr / QR, r = hr & (QR - 1);
         const bf16* src = q_rows + (size_t)(r0 + (r < n_rows ? r : 0)) * q_row_elems + (size_t)h * d;
         bf16* dst = q_s + (size_t)hr * L.qs;
@@ -377,7 +379,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // (a warp per row of the tile, a lane per 16 bytes: no divisions in the addresses)
-                for (int row = warp; row < G * BN; row += 8) {
+                for (int row = warp; row < G * BN; row += TALK_MMA_WARPS) {
                     const int g = row >> bn_log2, jj = row & (BN - 1), at = base_s[jj];
                     bf16* dst = kv_s + (size_t)row * L.kvs;
                     const bf16* src = kpool + ((size_t)(at < 0 ? 0 : at) + (size_t)g * JANIS_PAGE) * d;
@@ -391,9 +393,12 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 // ---- 1: raw scores of every head; a warp takes a head and up to four tiles of 8 keys, which share
                 //         the queries' fragments and run as four independent chains
                 {
-                    const int nts = BN / 8, groups = (nts + 3) / 4;
-                    for (int unit = warp; unit < H * groups; unit += 8) {
-                        const int g = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = g / rep;
+                    const int nts = BN / 8;
+                    int tg = 4;                               // tiles a unit: fewer where the warps would outnumber the units
+                    while (tg > 1 && H * ((nts + tg - 1) / tg) < TALK_MMA_WARPS) tg >>= 1;
+                    const int groups = (nts + tg - 1) / tg;
+                    for (int unit = warp; unit < H * groups; unit += TALK_MMA_WARPS) {
+                        const int g = unit / groups, nt0 = (unit % groups) * tg, n_here = min(tg, nts - nt0), kvh = g / rep;
                         float acc[4][4];
 #pragma unroll
                         for (int t = 0; t < 4; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
@@ -427,7 +432,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- 2a: the heads' scores mixed, the mask
-                for (int pair = tid; pair < QR * BN; pair += 256) {
+                for (int pair = tid; pair < QR * BN; pair += TALK_MMA_THREADS) {
                     const int r = pair >> bn_log2, c = pair & (BN - 1), j = j0 + c;
                     bool seen = r >= a && r < b && j <= pos_s[r];
                     if (seen && sh.block > 0) seen = j >= (pos_s[r] / sh.block) * sh.block;
@@ -451,7 +456,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- 2b: online softmax of every (head, row); P as bfloat16
-                for (int u = warp; u < HP * QR; u += 8) {
+                for (int u = warp; u < HP * QR; u += TALK_MMA_WARPS) {
                     const float* src = raw_s + ((size_t)h0 * QR + u) * L.rs;
                     const float s0 = lane < BN ? src[lane] : -CUDART_INF_F;
                     const float s1 = lane + 32 < BN ? src[lane + 32] : -CUDART_INF_F;
@@ -476,7 +481,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 }
                 __syncthreads();
                 // ---- values of the tile, into the keys' place
-                for (int row = warp; row < G * BN; row += 8) {
+                for (int row = warp; row < G * BN; row += TALK_MMA_WARPS) {
                     const int g = row >> bn_log2, jj = row & (BN - 1), at = base_s[jj];
                     bf16* dst = kv_s + (size_t)row * L.kvs;
                     const bf16* src = vpool + ((size_t)(at < 0 ? 0 : at) + (size_t)g * JANIS_PAGE) * dv;
@@ -491,7 +496,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                 //         P's fragments and run as four independent chains
                 {
                     const int nts = dv / 8, groups = (nts + 3) / 4;
-                    for (int unit = warp; unit < HP * groups; unit += 8) {
+                    for (int unit = warp; unit < HP * groups; unit += TALK_MMA_WARPS) {
                         const int h = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = (h0 + h) / rep;
                         const int r = lane >> 2;
                         const float c_lo = corr_s[h * QR + r], c_hi = QR == 16 ? corr_s[h * QR + r + 8] : 0.f;
@@ -543,7 +548,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     if (split) {
         // the chunk's share of row r0: per head the unnormalised sums, then the maximum and the denominator
         float* dst = partial + ((size_t)r0 * (gridDim.y / sh.hg) + blockIdx.y / sh.hg) * H * (dv + 2) + (size_t)h0 * (dv + 2);
-        for (int u = tid; u < HP * (dv + 2); u += 256) {
+        for (int u = tid; u < HP * (dv + 2); u += TALK_MMA_THREADS) {
             const int h = u / (dv + 2), c = u % (dv + 2);
             dst[u] = c < dv ? o_s[(size_t)h * QR * L.os + c] : (c == dv ? m_s[h * QR] : l_s[h * QR]);
         }
@@ -551,7 +556,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
     }
     // ---- the way out: divide, turn back by the row's position, round
     const int hv = dv >> 1;
-    for (int u = tid; u < n_rows * HP * hv; u += 256) {
+    for (int u = tid; u < n_rows * HP * hv; u += TALK_MMA_THREADS) {
         const int m = u % hv, h = (u / hv) % HP, r = u / (hv * HP);
         bf16* o_row = out + (size_t)(r0 + r) * H * dv + (size_t)(h0 + h) * dv;
         float lo = 0.f, hi = 0.f;
@@ -689,7 +694,7 @@ static int talk_mma_launch(const void* q_rows, int q_row_elems, const int* tok_p
         if (e != cudaSuccess) return fail("talk_attention: shared memory of %zu bytes refused: %s", bytes, cudaGetErrorString(e));
         most = bytes;
     }
-    const dim3 grid((T + sh.rows - 1) / sh.rows, (sh.chunk > 0 ? n_chunks : 1) * sh.hg), block(256);
+    const dim3 grid((T + sh.rows - 1) / sh.rows, (sh.chunk > 0 ? n_chunks : 1) * sh.hg), block(TALK_MMA_THREADS);
     if (launch_kernel("talk_attention", talk_attention_mma_kernel<HMAX>, grid, block, bytes, stream, 1, (const bf16*)q_rows,
                       q_row_elems, tok_pos, tok_seq, seq_slot, (const bf16*)kpool, (const bf16*)vpool, page_table,
                       table_stride, talk, inv_v, (bf16*)out, partial, T, sh))
