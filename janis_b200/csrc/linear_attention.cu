@@ -71,20 +71,47 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
     // A tile's q, k and decays travel through registers: a fixed number of elements a thread, all of their loads
     // asked for at once, and those of the next tile while this one is computed.  Tokens beyond the sequence's end
     // become q = k = v = 0 and decay 1, which change nothing, so a tile always runs all of its tokens.
-    constexpr int PER = GLA_TT * GLA_KS * DPT / (GLA_COLS * GLA_KS);
+    constexpr int NT = GLA_COLS * GLA_KS, WIDTH = GLA_KS * DPT;
+    constexpr int PER = GLA_TT * WIDTH / NT;               // elements of each of q, k and the decays a thread carries
+    constexpr int CH = WIDTH / 8;                          // pieces of 8 channels a token
     float qv[PER], kv[PER], av[PER], vv = 0.f;
+    // 16-byte loads (8 channels of one token a piece) where the rows allow it, else element by element (also at the
+    // smallest key sizes, where the pieces' places in shared memory would fall into few banks)
+    const bool vec = DPT >= 8 && d % 8 == 0 && g.row_elems % 8 == 0 && g.q_off % 8 == 0 && g.k_off % 8 == 0 &&
+                     (((uintptr_t)rows | (uintptr_t)decay) & 15) == 0 && sizeof(T) == 2;
     auto fetch = [&](int t0) {
+        if (vec) {
 #pragma unroll
-        for (int e = 0; e < PER; ++e) {
-            const int u = tid + e * (GLA_COLS * GLA_KS);
-            const int tt = u / (GLA_KS * DPT), c = u % (GLA_KS * DPT);
-            qv[e] = kv[e] = 0.f;
-            av[e] = 1.f;
-            if (t0 + tt < n_tok && c < d) {
-                const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
-                qv[e] = to_float(row[g.q_off + h * d + c]);
-                kv[e] = to_float(row[g.k_off + h * d + c]);
-                av[e] = decay[(size_t)(row0 + t0 + tt) * H * d + h * d + c];
+            for (int e = 0; e < PER / 8; ++e) {
+                const int u = tid + e * NT, tt = u / CH, c0 = (u % CH) * 8;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    qv[e * 8 + j] = kv[e * 8 + j] = 0.f;
+                    av[e * 8 + j] = 1.f;
+                }
+                if (t0 + tt < n_tok && c0 < d) {
+                    const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                    Vec16<T>::load(row + g.q_off + h * d + c0, &qv[e * 8]);      // (Vec16<bf16>: 8 values; this path is bfloat16 only)
+                    Vec16<T>::load(row + g.k_off + h * d + c0, &kv[e * 8]);
+                    const float4* dp = reinterpret_cast<const float4*>(decay + (size_t)(row0 + t0 + tt) * H * d + h * d + c0);
+                    const float4 d0 = dp[0], d1 = dp[1];
+                    av[e * 8 + 0] = d0.x; av[e * 8 + 1] = d0.y; av[e * 8 + 2] = d0.z; av[e * 8 + 3] = d0.w;
+                    av[e * 8 + 4] = d1.x; av[e * 8 + 5] = d1.y; av[e * 8 + 6] = d1.z; av[e * 8 + 7] = d1.w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < PER; ++e) {
+                const int u = tid + e * NT;
+                const int tt = u / WIDTH, c = u % WIDTH;
+                qv[e] = kv[e] = 0.f;
+                av[e] = 1.f;
+                if (t0 + tt < n_tok && c < d) {
+                    const T* row = rows + (size_t)(row0 + t0 + tt) * g.row_elems;
+                    qv[e] = to_float(row[g.q_off + h * d + c]);
+                    kv[e] = to_float(row[g.k_off + h * d + c]);
+                    av[e] = decay[(size_t)(row0 + t0 + tt) * H * d + h * d + c];
+                }
             }
         }
         vv = 0.f;
@@ -98,8 +125,16 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
         __syncthreads();                       // the tile before has been read
 #pragma unroll
         for (int e = 0; e < PER; ++e) {
-            const int u = tid + e * (GLA_COLS * GLA_KS);
-            const int tt = u / (GLA_KS * DPT), c = u % (GLA_KS * DPT);
+            int tt, c;
+            if (vec) {
+                const int u = tid + (e / 8) * NT;
+                tt = u / CH;
+                c = (u % CH) * 8 + e % 8;
+            } else {
+                const int u = tid + e * NT;
+                tt = u / WIDTH;
+                c = u % WIDTH;
+            }
             const int at = tt * TOK + (c / DPT) * RUN + c % DPT;
             q_s[at] = qv[e] * g.q_scale;
             k_s[at] = kv[e];
