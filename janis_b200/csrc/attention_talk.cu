@@ -244,7 +244,8 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
 //   3. O_h = O_h * corr + P_h V (mma.sync; V through ldmatrix.trans; items (head, 8 value columns) dealt to the
 //      warps), the accumulators living in shared memory as floats so that all sizes are run-time numbers.
 // Keys and values of a tile take turns in one buffer.  With QR = 8 the upper half of every 16-row operand repeats
-// the lower one and is dropped: big heads fit shared memory that way.  A decode step runs one row a CTA.
+// the lower one and is dropped: big heads fit shared memory that way.  A decode step runs one row a CTA and keeps that
+// row alone (QR = 1: every row of the 16-row operands repeats it).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
@@ -271,7 +272,7 @@ constexpr int TALK_MMA_WARPS = 16, TALK_MMA_THREADS = TALK_MMA_WARPS * 32;
 
 struct TalkMmaShape {
     int H, G, d, dv, block, sink;
-    int qr;             // rows of the operands kept (16 or 8)
+    int qr;             // rows of the operands kept (16 or 8; 1 in a decode step, whose CTAs own one row each)
     int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
     int bn;             // keys per tile (16, 32, 64)
     int chunk;          // keys per CTA of a decode step whose rows are cut over grid.y CTAs (0: a row's keys in one CTA)
@@ -420,6 +421,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
 #pragma unroll
                         for (int t = 0; t < 4; ++t)
                             if (t < n_here) {
+                                if (r >= QR) continue;        // (one row kept: the other rows of the operand repeat it)
                                 float* dst = raw_s + ((size_t)g * QR + r) * L.rs + (nt0 + t) * 8 + (lane & 3) * 2;
                                 dst[0] = acc[t][0] * sh.scale;
                                 dst[1] = acc[t][1] * sh.scale;
@@ -498,14 +500,15 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     const int nts = dv / 8, groups = (nts + 3) / 4;
                     for (int unit = warp; unit < HP * groups; unit += TALK_MMA_WARPS) {
                         const int h = unit / groups, nt0 = (unit % groups) * 4, n_here = min(4, nts - nt0), kvh = (h0 + h) / rep;
-                        const int r = lane >> 2;
+                        const bool mine = (lane >> 2) < QR;            // this lane's row of the sums is kept
+                        const int r = mine ? lane >> 2 : 0;
                         const float c_lo = corr_s[h * QR + r], c_hi = QR == 16 ? corr_s[h * QR + r + 8] : 0.f;
                         float* op = o_s + ((size_t)h * QR + r) * L.os + nt0 * 8 + (lane & 3) * 2;
                         float acc[4][4];
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
                             acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
-                            if (t < n_here) {
+                            if (t < n_here && mine) {
                                 acc[t][0] = op[t * 8] * c_lo;
                                 acc[t][1] = op[t * 8 + 1] * c_lo;
                                 if (QR == 16) {
@@ -529,7 +532,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                         }
 #pragma unroll
                         for (int t = 0; t < 4; ++t)
-                            if (t < n_here) {
+                            if (t < n_here && mine) {
                                 op[t * 8] = acc[t][0];
                                 op[t * 8 + 1] = acc[t][1];
                                 if (QR == 16) {
@@ -667,6 +670,20 @@ static TalkMmaShape talk_mma_shape(int H, int G, int d, int dv, int one_row, siz
     TalkMmaShape sh = {};
     if (H > 32 || d % 16 || dv % 8 || (dv & 1)) return sh;
     static const int order[6][2] = {{16, 64}, {16, 32}, {8, 64}, {8, 32}, {16, 16}, {8, 16}};
+    for (int hg = 1; one_row && hg <= 8; hg *= 2) {
+        // a decode step keeps one row of queries, scores and sums, so that several CTAs share an SM (tiles of
+        // 64, 32 or 16 keys: the largest that leaves room for two CTAs, else the largest that fits)
+        if (H % hg) break;
+        for (int pass = 0; pass < 2; ++pass)
+            for (int bn = 64; bn >= 16; bn >>= 1) {
+                const TalkMmaLayout L = talk_mma_layout(H, G, d, dv, 1, bn, H / hg);
+                if (L.total <= (size_t)(pass == 0 ? 110 : 220) * 1024) {
+                    sh.qr = 1; sh.bn = bn; sh.rows = 1; sh.hg = hg;
+                    *bytes = L.total;
+                    return sh;
+                }
+            }
+    }
     for (int hg = 1; hg <= 8; hg *= 2) {            // all heads' sums in one CTA where they fit, else the heads in groups
         if (H % hg) break;
         for (int i = 0; i < 6; ++i) {

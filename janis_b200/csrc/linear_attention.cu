@@ -1,7 +1,8 @@
 // Gated linear attention: a recurrent mixer with a matrix of state per head.
 //
 //   a_t  = sigmoid(z_t + b)^(1/tau)                           one decay per key channel (z_t: a projection of the input)
-//   S_t  = diag(a_t) S_{t-1} + k_t v_t^T                      S: [d, dv] float per head and sequence
+//   S_t  = diag(a_t) S_{t-1} + k_t v_t^T                      S: [d, dv] float per head and sequence (stored [dv, d]: a
+//                                                             lane's run of key channels of one column is contiguous)
 //   o_t  = S_t^T (q_t * q_scale)
 //
 // followed, in a second kernel, by an RMS norm of each head's o over dv, a gate silu(g) and the rounding to the
@@ -9,6 +10,8 @@
 // The state lives in the cache (one [H, d, dv] block per slot and line): a step loads it, runs its tokens in
 // order and writes it back, so a prompt, a prompt that continues and a decode step are the same launch.
 #include "common.cuh"
+
+#include <type_traits>
 
 namespace janis {
 
@@ -66,7 +69,7 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
 #pragma unroll
     for (int ii = 0; ii < DPT; ++ii) {
         const int i = ks * DPT + ii;
-        S[ii] = (st != nullptr && live && i < d) ? st[(size_t)i * dv + col] : 0.f;
+        S[ii] = (st != nullptr && live && i < d) ? st[(size_t)col * d + i] : 0.f;
     }
     // A tile's q, k and decays travel through registers: a fixed number of elements a thread, all of their loads
     // asked for at once, and those of the next tile while this one is computed.  Tokens beyond the sequence's end
@@ -145,27 +148,36 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
         if (t0 + GLA_TT < n_tok) fetch(t0 + GLA_TT);
         // the tile's tokens in order; each lane's share of o_t stays in a register until the tile is done
         float part_o[GLA_TT];
+        const int tt_n = min(GLA_TT, n_tok - t0);
+        // a whole tile runs without a test per token (its reads may then be asked for tokens ahead); the last tile of
+        // a prompt, and the single token of a decode step, skip the tokens that are not there
+        auto run_tokens = [&](auto guarded) {
 #pragma unroll
-        for (int tt = 0; tt < GLA_TT; ++tt) {
-            const float v = v_s[tt * GLA_COLS + tid / GLA_KS];
-            const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
-            const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
-            const float4* aa = reinterpret_cast<const float4*>(a_s + tt * TOK + ks * RUN);
-            float part[4] = {0.f, 0.f, 0.f, 0.f};           // four chains, added in a fixed order
+            for (int tt = 0; tt < GLA_TT; ++tt) {
+                part_o[tt] = 0.f;
+                if (decltype(guarded)::value && tt >= tt_n) continue;
+                const float v = v_s[tt * GLA_COLS + tid / GLA_KS];
+                const float4* qq = reinterpret_cast<const float4*>(q_s + tt * TOK + ks * RUN);
+                const float4* kk = reinterpret_cast<const float4*>(k_s + tt * TOK + ks * RUN);
+                const float4* aa = reinterpret_cast<const float4*>(a_s + tt * TOK + ks * RUN);
+                float part[4] = {0.f, 0.f, 0.f, 0.f};           // four chains, added in a fixed order
 #pragma unroll
-            for (int i4 = 0; i4 < DPT / 4; ++i4) {
-                const float4 q4 = qq[i4], k4 = kk[i4], a4 = aa[i4];
-                S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * v);
-                S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * v);
-                S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * v);
-                S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * v);
-                part[0] = fmaf(S[4 * i4 + 0], q4.x, part[0]);
-                part[1] = fmaf(S[4 * i4 + 1], q4.y, part[1]);
-                part[2] = fmaf(S[4 * i4 + 2], q4.z, part[2]);
-                part[3] = fmaf(S[4 * i4 + 3], q4.w, part[3]);
+                for (int i4 = 0; i4 < DPT / 4; ++i4) {
+                    const float4 q4 = qq[i4], k4 = kk[i4], a4 = aa[i4];
+                    S[4 * i4 + 0] = fmaf(a4.x, S[4 * i4 + 0], k4.x * v);
+                    S[4 * i4 + 1] = fmaf(a4.y, S[4 * i4 + 1], k4.y * v);
+                    S[4 * i4 + 2] = fmaf(a4.z, S[4 * i4 + 2], k4.z * v);
+                    S[4 * i4 + 3] = fmaf(a4.w, S[4 * i4 + 3], k4.w * v);
+                    part[0] = fmaf(S[4 * i4 + 0], q4.x, part[0]);
+                    part[1] = fmaf(S[4 * i4 + 1], q4.y, part[1]);
+                    part[2] = fmaf(S[4 * i4 + 2], q4.z, part[2]);
+                    part[3] = fmaf(S[4 * i4 + 3], q4.w, part[3]);
+                }
+                part_o[tt] = (part[0] + part[1]) + (part[2] + part[3]);
             }
-            part_o[tt] = (part[0] + part[1]) + (part[2] + part[3]);
-        }
+        };
+        if (tt_n == GLA_TT) run_tokens(std::false_type{});
+        else run_tokens(std::true_type{});
         // the 16 lanes of a column add their shares of all the tile's tokens at once: every stage halves the tokens
         // a lane still carries (the lanes whose bit is set keep the upper half), so 15 shuffles do what 64 would
         int n = GLA_TT;
@@ -195,7 +207,7 @@ gla_scan_kernel(const T* __restrict__ rows, GlaRows g, const float* __restrict__
 #pragma unroll
         for (int ii = 0; ii < DPT; ++ii) {
             const int i = ks * DPT + ii;
-            if (i < d) st[(size_t)i * dv + col] = S[ii];
+            if (i < d) st[(size_t)col * d + i] = S[ii];
         }
     }
 }

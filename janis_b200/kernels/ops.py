@@ -838,7 +838,7 @@ def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_
     """The recurrence of gated linear attention over the tokens each sequence brings to the step, in order:
     a = sigmoid(z + z_bias)^(1/tau) per key channel, S = diag(a) S + k v^T, o = S^T (q q_scale).
     rows [T, width] holds the projections (q [H, d] at q_off, k at k_off, v [H, dv] at v_off), z [T, H d] the
-    projected decay logits; state float32 [slots, H, d, dv] is read and written back for sequences whose slot is
+    projected decay logits; state float32 [slots, H, dv, d] (a column's key channels side by side) is read and written back for sequences whose slot is
     >= 0; o_out float32 [T, H dv]; decay float32 [T, H d] receives the decays (a kernel of its own forms them once
     for all the CTAs of a head; allocated here when not given)."""
     T, width = rows.shape
@@ -848,7 +848,7 @@ def gla_scan(rows, q_off: int, k_off: int, v_off: int, z, z_bias, seq_slot, seq_
     _t(rows, "rows", _FLOATS, (T, None))
     _t(z, "z", rows.dtype, (T, H * d))
     _t(z_bias, "z_bias", rows.dtype, (H * d,))
-    _t(state, "state", torch.float32, (None, H, d, dv))
+    _t(state, "state", torch.float32, (None, H, dv, d))
     _t(o_out, "o_out", torch.float32, (T, H * dv))
     for name, tab in (("seq_slot", seq_slot), ("seq_first_row", seq_first_row), ("seq_start", seq_start), ("seq_end", seq_end)):
         _t(tab, name, torch.int32)

@@ -11,7 +11,7 @@ side, multiplied by silu(Wg y) and projected by Wo.  Four projections of y are o
 q | k | v | g concatenated at load; the decay logits are two small products of their own.  Decays (from the
 logits on), the state and o are float32 whatever the activations are.
 
-The state is a fixed-size part of a cache line (`StateNeed`): a step loads it, runs its tokens in order and
+The state is a fixed-size part of a cache line (`StateNeed`, stored as S^T: [heads, dv, d]): a step loads it, runs its tokens in order and
 writes it back, so a prompt, a prompt that continues and a decode step are one code path; sequences without a
 slot (padding) start from zero and store nothing.
 """
@@ -53,7 +53,7 @@ class GatedLinearAttention(Mixer):
                 n["norm"]: TensorSpec((dv,), init_std=0.1)}
 
     def cache_needs(self):
-        return {"state": StateNeed((self.n_heads, self.key_dim, self.value_dim), torch.float32)}
+        return {"state": StateNeed((self.n_heads, self.value_dim, self.key_dim), torch.float32)}     # S^T per head
 
     def prompt_flops(self, n_tokens: int) -> float:
         return 5.0 * self.n_heads * self.key_dim * self.value_dim * n_tokens      # decay, outer product, read-out

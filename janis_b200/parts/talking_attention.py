@@ -102,8 +102,8 @@ class TalkingHeadsAttention(Mixer):
         decode = ctx.mode == "decode"
         max_keys, n_chunks, scratch = 0, 1, None
         if decode:
-            # a decode row's keys over several CTAs when the rows alone would leave most of the GPU idle: about an
-            # SM's worth of CTAs in all, none with fewer than 128 keys (the bound on the lengths is the host's)
+            # a decode row's keys over several CTAs when the rows alone would leave most of the GPU idle: about a
+            # CTA an SM in all, none with fewer than 128 keys (the bound on the lengths is the host's)
             max_keys = min(self.block, ctx.len_bound) if self.block else ctx.len_bound
             n_chunks = max(1, min(rt.sm_count // max(T, 1), -(-max_keys // 128), 64))
             n = ops.talk_attention_scratch_floats(T, n_chunks, H, dv)

@@ -388,7 +388,7 @@ def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_
         slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
         if n <= 0:
             continue
-        S = state[slot].double().clone() if slot >= 0 else torch.zeros(H, d, dv, dtype=torch.float64)
+        S = state[slot].double().transpose(1, 2).clone() if slot >= 0 else torch.zeros(H, d, dv, dtype=torch.float64)
         for t in range(row0, row0 + n):
             row = rows[t].double()
             q = row[q_off:q_off + H * d].view(H, d) * q_scale
@@ -398,7 +398,7 @@ def gla_scan(rows, q_off, k_off, v_off, z, z_bias, seq_slot, seq_first_row, seq_
             S = a[:, :, None] * S + k[:, :, None] * v[:, None, :]
             o_out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1).float()
         if slot >= 0:
-            state[slot] = S.float()
+            state[slot] = S.transpose(1, 2).float()          # stored [H, dv, d]
     return o_out
 
 

@@ -330,7 +330,7 @@ def test_recurrence_kernel_against_its_statement(dtype, H, d, dv, tau):
     T = sum(lens)
     width = 2 * H * d + 2 * H * dv
     b2 = (1.0 + torch.randn(H * d, generator=g)).to(dtype)
-    state_cpu = torch.zeros(4, H, d, dv)
+    state_cpu = torch.zeros(4, H, dv, d)
     state_dev = state_cpu.clone().cuda()
     slots = torch.tensor([2, -1, 0], dtype=torch.int32)
     first = torch.tensor([0, 1, 18], dtype=torch.int32)
