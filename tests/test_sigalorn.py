@@ -239,7 +239,8 @@ def _paged(n_seq, lens, G, d, dv, dtype, seed, spare=3):
     (4, 2, 32, 16, 24, True, True, True), (6, 3, 64, 48, 190, True, True, True), (3, 1, 24, 40, 1, True, False, False),
     (8, 2, 64, 64, 128, False, True, True), (2, 2, 16, 8, 0, False, False, True), (5, 5, 8, 6, 7, True, True, False),
     (8, 4, 256, 256, 100, True, True, True), (20, 10, 32, 48, 65, True, True, True),
-    (16, 8, 256, 256, 90, True, True, True), (32, 16, 128, 128, 0, False, True, False)])    # heads in groups over CTAs
+    (16, 8, 256, 256, 90, True, True, True), (32, 16, 128, 128, 0, False, True, False),      # heads in groups over CTAs
+    (1, 1, 16, 8, 5, True, True, True), (3, 1, 32, 24, 50, False, False, False)])
 def test_attention_kernel_against_its_statement(dtype, H, G, d, dv, block, sink, talk, turn):
     """Queries at chosen positions (a block's first and last place, a page's border, far into the sequence) over
     scattered pages; one far key made to stand out for each query."""
