@@ -140,7 +140,8 @@ def prefill_flops(model, n_tokens: int) -> float:
     layer's mixer says it computes beyond its products (attention: scores and weighted sums)."""
     flops = 0.0
     for name, spec in model.tensor_specs().items():
-        if len(spec.shape) == 2 and name != getattr(model.embedding, "table_name", None):
+        if len(spec.shape) == 2 and name not in (getattr(model.embedding, "table_name", None),
+                                                    getattr(model.head, "table_name", None)):       # (the head: below)
             flops += 2.0 * n_tokens * spec.shape[0] * spec.shape[1]
     for call in model.schedule:
         flops += float(model.blocks[call.layer].mixer.prompt_flops(n_tokens))
