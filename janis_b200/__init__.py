@@ -13,9 +13,11 @@ of parts are registered by name (`register_architecture`, `parts.registry`).
 from .config.base import ConfigError
 from .config.gemma2 import Gemma2Config
 from .config.sigalorn import SigalornConfig
+from .config.nosolix import NosolixConfig
 from .registry import architectures, register_architecture, resolve, unregister_architecture
 from .models import gemma2 as _gemma2            # registers Gemma2ForCausalLM
 from .models import sigalorn as _sigalorn        # registers Sigalorn
+from .models import nosolix as _nosolix          # registers Nosolix
 from .engine.engine import Engine, build_model, from_config, load, open, write_random_model
 from .engine.step import StepEntry, StepError
 from .engine.generate import Reply
@@ -25,5 +27,5 @@ from .weights.loader import WeightsError
 __version__ = "0.1.0"
 
 __all__ = ["open", "load", "from_config", "write_random_model", "build_model", "Engine", "StepEntry", "StepError",
-           "Reply", "SamplingParams", "Gemma2Config", "ConfigError", "WeightsError", "register_architecture",
+           "Reply", "SamplingParams", "Gemma2Config", "SigalornConfig", "NosolixConfig", "ConfigError", "WeightsError", "register_architecture",
            "unregister_architecture", "architectures", "resolve", "__version__"]

@@ -209,11 +209,12 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 
 // Activations of a dense feed-forward, by the codes of bias_act: 0 nothing; 1 xIELU with a_pos = softplus(p) and
 // a_neg = 1/2 + softplus(q) formed on the host (z > 0: a_pos z^2 + z/2; z <= 0: a_neg (e^z - 1 - z) + z/2);
-// 2 the tanh form of gelu; 3 silu.
+// 2 the tanh form of gelu; 3 silu; 4 the square of relu.
 __device__ __forceinline__ float dense_act(float z, int act, float a_pos, float a_neg) {
     if (act == 1) return z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
     if (act == 2) return gelu_tanh(z);
     if (act == 3) return z / (1.0f + expf(-z));
+    if (act == 4) return z > 0.f ? z * z : 0.f;
     return z;
 }
 

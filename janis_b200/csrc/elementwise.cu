@@ -589,7 +589,7 @@ JANIS_EXPORT int janis_gated_act(const void* gu, void* out, int dtype, int rows,
 JANIS_EXPORT int janis_bias_act(void* x, const void* bias, int dtype, int rows, int N, int act, float a_pos, float a_neg,
                                 cudaStream_t stream) {
     if (rows <= 0 || N <= 0) return 0;
-    if (act < 0 || act > 3) return fail("bias_act: unknown activation %d", act);
+    if (act < 0 || act > 4) return fail("bias_act: unknown activation %d", act);
     const size_t n = (size_t)rows * N;
     const int vec = dtype == JANIS_F32 ? 4 : 8;
     if (N % vec == 0 && (((uintptr_t)x | (uintptr_t)bias) & 15) == 0 && (dtype == JANIS_F32 || dtype == JANIS_BF16)) {

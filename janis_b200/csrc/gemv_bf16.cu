@@ -452,7 +452,7 @@ JANIS_EXPORT int janis_gemv_bf16_bias_act(const void* x, const void* W, void* ou
     if (M <= 0 || N <= 0) return 0;
     if (M > 64) return fail("gemv_bf16_bias_act: at most 64 rows, found %d", M);
     if (K <= 0 || K % 8) return fail("gemv_bf16_bias_act: K must be a positive multiple of 8, found %d", K);
-    if (act < 0 || act > 3) return fail("gemv_bf16_bias_act: unknown activation %d", act);
+    if (act < 0 || act > 4) return fail("gemv_bf16_bias_act: unknown activation %d", act);
     if (((uintptr_t)x | (uintptr_t)W) & 15) return fail("gemv_bf16_bias_act: operands must be 16-byte aligned");
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;

@@ -281,7 +281,7 @@ def gated_act(gu, out, act: int = ACT_GELU_TANH, group: int = GATE_GROUP):
     return out
 
 
-ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN = 0, 1, 2, 3
+ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN, ACT_RELU2 = 0, 1, 2, 3, 4
 
 
 def bias_act(x, bias, act: int = ACT_NONE, a_pos: float = 0.0, a_neg: float = 0.0):

@@ -6,7 +6,8 @@ is added:  r = Mixer(N_in(x)); h = x + N_post_mixer(r); r = FF(N_pre_ff(h));
 out = h + N_post_ff(r).  Without a feed-forward (`feed_forward=None`) a layer is the first line alone.
 
 `PreNormBlock` is the usual arrangement without the norms after the sublayers
-(`qwen/block.go:58-61`): h = x + Mixer(N_in(x)); out = h + FF(N_pre_ff(h)).
+(`qwen/block.go:58-61`): h = x + Mixer(N_in(x)); out = h + FF(N_pre_ff(h)); without a feed-forward the first
+line alone.
 
 The residual stream is float32 and is updated in place.  A block may be handed
 its first norm's output (computed by the block before it together with that
@@ -50,12 +51,16 @@ class SandwichBlock(Block):
 
 
 class PreNormBlock(Block):
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, input_norm: Norm, pre_ff_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward | None, input_norm: Norm, pre_ff_norm: Norm | None = None):
+        if feed_forward is not None and pre_ff_norm is None:
+            raise ValueError("a block with a feed-forward needs the norm before it")
         self.mixer, self.feed_forward = mixer, feed_forward
         self.first_norm = input_norm
         self.pre_ff_norm = pre_ff_norm
 
     def sub_parts(self):
+        if self.feed_forward is None:
+            return [self.first_norm, self.mixer]
         return [self.first_norm, self.mixer, self.pre_ff_norm, self.feed_forward]
 
     def forward(self, h, ctx: StepContext, line, y_in=None, next_norm: Norm | None = None):
@@ -63,6 +68,9 @@ class PreNormBlock(Block):
         dt = ctx.rt.dtype
         y = y_in if y_in is not None else self.first_norm.forward(h, ctx, ctx.ws.buf("block.y", (T, H), dt))
         r = self.mixer.forward(y, ctx, line)
+        if self.feed_forward is None:
+            return h, plain_residual_add(h, r, ctx, next_norm,
+                                         ctx.ws.buf("block.y", (T, H), dt) if next_norm is not None else None)
         y = plain_residual_add(h, r, ctx, self.pre_ff_norm, ctx.ws.buf("block.y", (T, H), dt))
         r = self.feed_forward.forward(y, ctx)
         y_next = plain_residual_add(h, r, ctx, next_norm,

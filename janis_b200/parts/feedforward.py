@@ -86,7 +86,7 @@ def _softplus(v: float) -> float:
 class DenseMLP(FeedForward):
     """down(act(up(x) + b_up)) + b_down, the biases optional.
 
-    act: "gelu_tanh", "silu", or "xielu", a piecewise activation with two learnt numbers (p, q) per layer, stored
+    act: "gelu_tanh", "silu", "relu2" (the square of relu), or "xielu", a piecewise activation with two learnt numbers (p, q) per layer, stored
     as a tensor of two values under names["act"]:
         z > 0:   softplus(p) z^2 + z/2
         z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z/2
@@ -94,8 +94,8 @@ class DenseMLP(FeedForward):
 
     def __init__(self, hidden: int, intermediate: int, names: dict[str, str], act: str = "xielu",
                  init_std: float = 0.02):
-        if act not in ("xielu", "gelu_tanh", "silu"):
-            raise ValueError(f"unknown activation {act!r} (known: gelu_tanh, silu, xielu)")
+        if act not in ("xielu", "gelu_tanh", "silu", "relu2"):
+            raise ValueError(f"unknown activation {act!r} (known: gelu_tanh, relu2, silu, xielu)")
         for k in ("up", "down"):
             if k not in names:
                 raise ValueError(f"feed-forward needs the checkpoint name of its {k!r} projection")
@@ -134,7 +134,7 @@ class DenseMLP(FeedForward):
         T = ctx.n_tok
         a = ws.buf("ffn.act", (T, self.intermediate), rt.dtype)
         out = ws.buf("ffn.out", (T, self.hidden), rt.dtype)
-        kind = {"xielu": ops.ACT_XIELU, "gelu_tanh": ops.ACT_GELU, "silu": ops.ACT_SILU_PLAIN}[self.act]
+        kind = {"xielu": ops.ACT_XIELU, "gelu_tanh": ops.ACT_GELU, "silu": ops.ACT_SILU_PLAIN, "relu2": ops.ACT_RELU2}[self.act]
         if (rt.dtype == torch.bfloat16 and T <= ops.GEMV_FAST_ROWS and self.hidden % 8 == 0 and self.intermediate % 8 == 0
                 and hasattr(ops, "gemv_bf16_bias_act")):
             # few rows: bias and activation in the epilogue of the skinny products (the same bits as the two kernels)

@@ -1,9 +1,12 @@
-"""RMS norm with a weight offset.
+"""Norms of the residual stream: RMS norm with a weight offset, and Dynamic Tanh.
 
 y = x / sqrt(mean(x^2) + eps) * (offset + w).  Gemma2 stores w and uses 1 + w
 (`gemma/gemma.go:22-28`); offset 0 is the usual RMS norm (`qwen/norm.go:10-27`).
 eps lies inside the root, added to the mean (`cpu/cpu_ops.go:145-162`).  The
 sum of squares, the root and offset + w are float32 whatever the model's dtype.
+
+`DynamicTanh` takes no statistics of the row: y = tanh(alpha x) * w + b with a stored scalar alpha and vectors w
+and b, element by element, in float32.
 """
 from __future__ import annotations
 
@@ -43,9 +46,46 @@ class RMSNorm(Norm):
         return next_norm.forward(h, ctx, out)
 
 
+class DynamicTanh(Norm):
+    """y = tanh(alpha x) * w + b.  Tensors: `weight_name` [width], `<weight_name>.b` [width], `<weight_name>.alpha` []
+    (other names through `bias_name` and `alpha_name`)."""
+
+    def __init__(self, width: int, weight_name: str, bias_name: str | None = None, alpha_name: str | None = None,
+                 init_std: float = 0.1, init_mean: float = 1.0, init_alpha: float = 0.5):
+        self.width = width
+        self.weight_name = weight_name
+        self.bias_name = bias_name or weight_name + ".b"
+        self.alpha_name = alpha_name or weight_name + ".alpha"
+        self.init_std, self.init_mean, self.init_alpha = init_std, init_mean, init_alpha
+        self.weight = self.bias = None      # float32
+        self.alpha = 0.0
+
+    def tensor_specs(self):
+        return {self.weight_name: TensorSpec((self.width,), init_std=self.init_std, init_mean=self.init_mean),
+                self.bias_name: TensorSpec((self.width,), init_std=self.init_std),
+                self.alpha_name: TensorSpec((), init_std=0.1 * self.init_alpha, init_mean=self.init_alpha)}
+
+    def load(self, store, rt: Runtime):
+        self.weight = store.get(self.weight_name).to(torch.float32).contiguous()
+        self.bias = store.get(self.bias_name).to(torch.float32).contiguous()
+        self.alpha = float(store.get(self.alpha_name).to(torch.float32).reshape(()).item())
+
+    def forward(self, x, ctx: StepContext, out, rows=None):
+        return ctx.rt.ops.dyt_norm(x, None, self.alpha, self.weight, self.bias, out, rows)
+
+    def after_add(self, h, r, ctx: StepContext, out):
+        """h += r and out = self(h) in one pass over the stream."""
+        return ctx.rt.ops.dyt_norm(h, r, self.alpha, self.weight, self.bias, out)
+
+    def residual_add(self, h, r, ctx: StepContext, next_norm: Norm | None = None, out=None):
+        raise NotImplementedError("Dynamic Tanh stands before a sublayer, not after one")
+
+
 def plain_residual_add(h, r, ctx: StepContext, next_norm: Norm | None = None, out=None):
     """h += r for blocks without a norm after the sublayer; out = next_norm(h) when given."""
     if isinstance(next_norm, RMSNorm):
         return ctx.rt.ops.add_rmsnorm(h, r, None, 0.0, next_norm.weight, next_norm.eps, out)
+    if hasattr(next_norm, "after_add"):
+        return next_norm.after_add(h, r, ctx, out)
     ctx.rt.ops.add_rmsnorm(h, r, None, 0.0)
     return next_norm.forward(h, ctx, out) if next_norm is not None else None

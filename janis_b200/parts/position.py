@@ -21,8 +21,28 @@ import torch
 from .base import PositionEncoding, Runtime, StepContext
 
 
+def band_scaled_frequencies(inv_freq, factor: float, low: float, high: float, original: float):
+    """Inverse frequencies rescaled by wavelength, for a model that was trained on contexts of `original`
+    positions and runs on longer ones: a component whose wavelength 2 pi / f is shorter than original / high is
+    kept; one longer than original / low is slowed down to f / factor; in between the two are blended with
+    s = (original / wavelength - low) / (high - low): (1 - s) f / factor + s f.  Computed in float64."""
+    out = []
+    for f in inv_freq:
+        f = float(f)
+        wave = 2.0 * math.pi / f
+        if wave < original / high:
+            out.append(f)
+        elif wave > original / low:
+            out.append(f / factor)
+        else:
+            s = (original / wave - low) / (high - low)
+            out.append((1.0 - s) * f / factor + s * f)
+    return out
+
+
 class RotaryEncoding(PositionEncoding):
-    def __init__(self, head_dim: int, base: float, rotary_dims: int | None = None, inv_freq=None):
+    def __init__(self, head_dim: int, base: float, rotary_dims: int | None = None, inv_freq=None,
+                 band_scaling: dict | None = None):
         rot = head_dim if rotary_dims is None else int(rotary_dims)
         if rot % 2 or rot < 0 or rot > head_dim:
             raise ValueError(f"rotary width {rot} must be even and at most the head size {head_dim}")
@@ -30,7 +50,9 @@ class RotaryEncoding(PositionEncoding):
         self.rot = rot
         self.base = float(base)
         if inv_freq is None:
-            inv_freq = [np.float32(math.pow(self.base, -float(2 * i) / float(rot))) for i in range(rot // 2)]
+            inv_freq = [math.pow(self.base, -float(2 * i) / float(rot)) for i in range(rot // 2)]
+            if band_scaling:          # {"factor", "low", "high", "original"}: see band_scaled_frequencies
+                inv_freq = band_scaled_frequencies(inv_freq, **band_scaling)
         self._inv_host = np.asarray(inv_freq, dtype=np.float32)
         if self._inv_host.shape != (rot // 2,):
             raise ValueError("inv_freq must hold rotary_dims / 2 values")

@@ -44,15 +44,23 @@ def _register_builtin() -> None:
     from .feedforward import DenseMLP, GatedMLP
     from .linear_attention import GatedLinearAttention
     from .talking_attention import TalkingHeadsAttention
-    from .norm import RMSNorm
+    from .moe import RoutedExperts
+    from .norm import DynamicTanh, RMSNorm
+    from .parallel import ParallelMixers
+    from .state_space import DualityMixer, SelectiveScanMixer
     from .position import NoPosition, RotaryEncoding
 
     register("mixer", "softmax_attention", SoftmaxAttention)
     register("mixer", "talking_heads_attention", TalkingHeadsAttention)   # heads mixed before the softmax, sink, block mask
     register("mixer", "gated_linear_attention", GatedLinearAttention)     # a matrix of state per head, decays per key channel
+    register("mixer", "selective_scan", SelectiveScanMixer)               # a state per channel, step sizes through a low rank
+    register("mixer", "state_space_duality", DualityMixer)                # a scalar decay per head, grouped B and C
+    register("mixer", "parallel", ParallelMixers)                         # branches on one input, normed and averaged
     register("feed_forward", "gated_mlp", GatedMLP)
     register("feed_forward", "dense_mlp", DenseMLP)                       # up, activation, down, with biases
+    register("feed_forward", "routed_experts", RoutedExperts)             # a router over small gated experts, a shared one
     register("norm", "rms_norm", RMSNorm)
+    register("norm", "dynamic_tanh", DynamicTanh)
     register("position", "rotary", RotaryEncoding)
     register("position", "none", NoPosition)
     register("block", "sandwich", SandwichBlock)

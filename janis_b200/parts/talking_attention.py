@@ -9,9 +9,13 @@ and values of dv:
     o_h[i]      = sum_j p_h[i, j] v[j]
 
 over the keys j <= i that lie in the query's block of `block` positions (block 0: all of them; blocks are counted
-from the sequence's first position).  `sink` adds 1 to the denominator: a key of score 0 that has no value.  With a
+from the sequence's first position) and, with a `window`, among the query's last `window` positions (i - j < window:
+the query's own and the window - 1 before it).  `sink` adds 1 to the denominator: a key of score 0 that has no value.  With a
 `value_position` the values are rotated by their own position before they are cached (over all dv features) and
 each head's output is turned back by the query's position, so that o depends on relative positions only.
+
+With a gate (names["g"]) the heads side by side are multiplied, element by element, by sigmoid(Wg y) before the
+output projection; Wg's rows stand behind the other projections' in the one product.
 
 Keys and values live in a paged cache line with separate head sizes.  A step writes its keys and values first
 and then attends over the line alone, so a prompt, a prompt that continues, a decode step and a layer that reads
@@ -31,7 +35,7 @@ from .position import RotaryEncoding
 class TalkingHeadsAttention(Mixer):
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, scale: float,
                  position: RotaryEncoding, names: dict[str, str], value_position: RotaryEncoding | None = None,
-                 block: int = 0, sink: bool = False, own_kv: bool = True, init_std: float = 0.02):
+                 block: int = 0, sink: bool = False, own_kv: bool = True, init_std: float = 0.02, window: int = 0):
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} query heads do not divide over {n_kv_heads} key/value heads")
         need = ("q", "k", "v", "o") if own_kv else ("q", "o")
@@ -44,6 +48,9 @@ class TalkingHeadsAttention(Mixer):
         self.key_dim, self.value_dim = key_dim, value_dim
         self.scale = float(scale)
         self.block = int(block or 0)
+        self.window = int(window or 0)
+        if self.window < 0:
+            raise ValueError(f"a window holds at least one position, found {window}")
         self.sink = bool(sink)
         self.own_kv = bool(own_kv)
         self.position, self.value_position = position, value_position
@@ -59,6 +66,8 @@ class TalkingHeadsAttention(Mixer):
             specs[n["v"]] = TensorSpec((G * dv, W), init_std=s)
         if "talk" in n:
             specs[n["talk"]] = TensorSpec((H, H), init_std=H ** -0.5)
+        if "g" in n:
+            specs[n["g"]] = TensorSpec((H * dv, W), init_std=s)
         return specs
 
     def sub_parts(self):
@@ -71,15 +80,22 @@ class TalkingHeadsAttention(Mixer):
         B = self.block or n_tokens
         full, rest = divmod(n_tokens, B)
         seen = full * (B * (B + 1) // 2) + rest * (rest + 1) // 2         # (query, key) pairs
+        if self.window and not self.block:
+            w = min(self.window, n_tokens)
+            seen = w * (w + 1) // 2 + (n_tokens - w) * w
         return seen * 2.0 * self.n_heads * (self.key_dim + self.value_dim + ("talk" in self.names) * self.n_heads)
 
     def load(self, store, rt: Runtime):
         n = self.names
+        gated = ("g",) if "g" in n else ()
         if self.own_kv:
-            q, k, v = (store.get(n[x], rt.dtype) for x in ("q", "k", "v"))
-            self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
-            del q, k, v
-            store.drop(n["q"], n["k"], n["v"])
+            mats = [store.get(n[x], rt.dtype) for x in ("q", "k", "v") + gated]
+            self.w_qkv = torch.cat(mats, dim=0).contiguous()
+            del mats
+            store.drop(*(n[x] for x in ("q", "k", "v") + gated))
+        elif gated:
+            self.w_qkv = torch.cat([store.get(n["q"], rt.dtype), store.get(n["g"], rt.dtype)], dim=0).contiguous()
+            store.drop(n["q"], n["g"])
         else:
             self.w_qkv = store.get(n["q"], rt.dtype).contiguous()
         self.w_o = store.get(n["o"], rt.dtype).contiguous()
@@ -91,7 +107,8 @@ class TalkingHeadsAttention(Mixer):
         if kv.write != self.own_kv:
             raise ValueError("the schedule lets a layer with keys and values of its own only read a line, or the reverse")
         T, H, G, d, dv = ctx.n_tok, self.n_heads, self.n_kv_heads, self.key_dim, self.value_dim
-        width = H * d + (G * (d + dv) if self.own_kv else 0)
+        g_off = H * d + (G * (d + dv) if self.own_kv else 0)         # where the gate's logits start in a row
+        width = g_off + (H * dv if "g" in self.names else 0)
         rows = ws.buf("tattn.rows", (T, width), rt.dtype)
         rt.linear(x, self.w_qkv, rows)
         inv_v = self.value_position.inv_freq if self.value_position is not None else None
@@ -105,10 +122,14 @@ class TalkingHeadsAttention(Mixer):
             # a decode row's keys over several CTAs when the rows alone would leave most of the GPU idle: about a
             # CTA an SM in all, none with fewer than 128 keys (the bound on the lengths is the host's)
             max_keys = min(self.block, ctx.len_bound) if self.block else ctx.len_bound
+            if self.window:
+                max_keys = min(max_keys, self.window)
             n_chunks = max(1, min(rt.sm_count // max(T, 1), -(-max_keys // 128), 64))
             n = ops.talk_attention_scratch_floats(T, n_chunks, H, dv)
             scratch = ws.buf("tattn.partial", (n,), torch.float32) if n else None
         ops.talk_attention(rows, ctx.tok_pos, ctx.tok_seq, ctx.seq_slot, kv.k, kv.v, kv.table, self.talk, inv_v, att,
                            H, G, d, dv, self.scale, self.block, self.sink, one_row=decode, max_keys=max_keys,
-                           n_chunks=n_chunks, scratch=scratch)
+                           n_chunks=n_chunks, scratch=scratch, window=self.window)
+        if "g" in self.names:
+            ops.sigmoid_gate(att, rows, g_off)
         return rt.linear(att, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

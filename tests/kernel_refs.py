@@ -296,7 +296,7 @@ def mask_tokens(logits, ids):
 # mixers with run-time sizes
 # ---------------------------------------------------------------------------
 
-ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN = 0, 1, 2, 3
+ACT_NONE, ACT_XIELU, ACT_GELU, ACT_SILU_PLAIN, ACT_RELU2 = 0, 1, 2, 3, 4
 
 
 def bias_act(x, bias, act=ACT_NONE, a_pos=0.0, a_neg=0.0):
@@ -309,6 +309,8 @@ def bias_act(x, bias, act=ACT_NONE, a_pos=0.0, a_neg=0.0):
         z = _act(z, ACT_GELU_TANH)
     elif act == ACT_SILU_PLAIN:
         z = _act(z, ACT_SILU)
+    elif act == ACT_RELU2:
+        z = torch.clamp(z, min=0.0) ** 2
     x.copy_(z.to(x.dtype))
     return x
 
@@ -352,7 +354,7 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot, inv_v, H, G,
 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H, G, d, dv, scale,
-                   block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None):
+                   block=0, sink=False, one_row=False, max_keys=0, n_chunks=1, scratch=None, window=0):
     T = q_rows.shape[0]
     rep = H // G
     for t in range(T):
@@ -361,6 +363,8 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
             out[t] = 0
             continue
         first = (pos // block) * block if block > 0 else 0
+        if window > 0:
+            first = max(first, pos - window + 1)
         js = list(range(first, pos + 1))
         pages = [int(page_table[slot, j // PAGE]) for j in js]
         k = torch.stack([kpool[p, :, j % PAGE] for p, j in zip(pages, js)]).double()       # [n, G, d]
@@ -410,4 +414,121 @@ def head_norm_gate(o, rows, g_off, weight, eps, out, H, dv):
         g = rows[:, g_off:g_off + H * dv].double().view(T, H, dv)
         y = y * g * torch.sigmoid(g)
     out.copy_(y.reshape(T, H * dv).to(out.dtype))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Dynamic Tanh, state-space mixers, parallel branches, mixture of experts
+# ---------------------------------------------------------------------------
+
+def dyt_norm(h, res, alpha, weight, bias, out, rows=None):
+    """h += res (when given; float32 in place), then out = tanh(alpha h) * weight + bias over the rows asked for."""
+    if res is not None:
+        h.copy_((h.double() + res.double()).float())
+    src = h if rows is None else h[rows.long()]
+    out.copy_((torch.tanh(float(np.float32(alpha)) * src.double()) * weight.double() + bias.double()).to(out.dtype))
+    return out
+
+
+def causal_conv_silu(rows, col_off, channels, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start, seq_end,
+                     n_seq, out):
+    taps = weight.shape[1]
+    w, b = weight.double(), bias.double()
+    for s in range(n_seq):
+        slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
+        if n <= 0:
+            continue
+        x = rows[row0:row0 + n, col_off:col_off + channels].double()
+        past = state[slot, :taps - 1].double() if slot >= 0 else torch.zeros(taps - 1, channels, dtype=torch.float64)
+        full = torch.cat([past, x], dim=0)                                  # local index i lives at i + taps - 1
+        acc = b.expand(n, channels).clone()
+        for j in range(taps):
+            acc += w[:, taps - 1 - j] * full[taps - 1 - j:taps - 1 - j + n]
+        out[row0:row0 + n] = (acc * torch.sigmoid(acc)).to(out.dtype)
+        if slot >= 0 and taps > 1:
+            state[slot, :taps - 1] = full[n:n + taps - 1].float()
+    return out
+
+
+def selective_scan(u, u_off, dt, dt_off, dt_bias, A, a_per_state, bc, b_off, c_off, D, z, z_off, seq_slot, seq_first_row,
+                   seq_start, seq_end, n_seq, state, out, C, N, ch_per_head, ch_per_group):
+    heads = C // ch_per_head
+    Af = A.double() if a_per_state else A.double()[:, None].expand(heads, N)
+    Ac = Af.repeat_interleave(ch_per_head, dim=0)                           # [C, N]
+    Dc = D.double().repeat_interleave(ch_per_head)
+    for s in range(n_seq):
+        slot, row0, n = int(seq_slot[s]), int(seq_first_row[s]), int(seq_end[s]) - int(seq_start[s])
+        if n <= 0:
+            continue
+        S = state[slot].double().clone() if slot >= 0 else torch.zeros(C, N, dtype=torch.float64)
+        for t in range(row0, row0 + n):
+            raw = dt[t, dt_off:dt_off + heads].double() + dt_bias.double()
+            delta = torch.logaddexp(raw, torch.zeros_like(raw)).repeat_interleave(ch_per_head)       # [C]
+            x = u[t, u_off:u_off + C].double()
+            groups = C // ch_per_group
+            B = bc[t, b_off:b_off + groups * N].double().view(groups, N).repeat_interleave(ch_per_group, dim=0)
+            Cm = bc[t, c_off:c_off + groups * N].double().view(groups, N).repeat_interleave(ch_per_group, dim=0)
+            S = torch.exp(delta[:, None] * Ac) * S + (delta * x)[:, None] * B
+            o = (S * Cm).sum(-1) + Dc * x
+            if z is not None:
+                g = z[t, z_off:z_off + C].double()
+                o = o * g * torch.sigmoid(g)
+            out[t] = o.to(out.dtype)
+        if slot >= 0:
+            state[slot] = S.float()
+    return out
+
+
+def gate_group_norm(o, rows, z_off, weight, eps, n_groups, out):
+    T, C = o.shape
+    g = rows[:, z_off:z_off + C].double()
+    x = (o.double() * g * torch.sigmoid(g)).view(T, n_groups, C // n_groups)
+    y = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    out.copy_((y.reshape(T, C) * weight.double()).to(out.dtype))
+    return out
+
+
+def rmsnorm_accumulate(x, weight, eps, scale, acc, first=False):
+    y = _norm(x, weight, eps) * scale
+    acc.copy_((y if first else acc.double() + y).float())
+    return acc
+
+
+def sigmoid_gate(x, rows, g_off):
+    g = rows[:, g_off:g_off + x.shape[1]].double()
+    x.copy_((x.double() * torch.sigmoid(g)).to(x.dtype))
+    return x
+
+
+def moe_route(z, correction, n_experts, group_count, group_keep, top, scale, shared_gate, out):
+    T = z.shape[0]
+    s = torch.sigmoid(z[:, :n_experts].double())
+    c = s + correction.double()
+    per = n_experts // group_count
+    out.zero_()
+    for t in range(T):
+        gs = [sum(sorted(c[t, g * per:(g + 1) * per].tolist(), reverse=True)[:2]) for g in range(group_count)]
+        kept = sorted(range(group_count), key=lambda g: (-gs[g], g))[:group_keep]
+        cand = [e for g in sorted(kept) for e in range(g * per, (g + 1) * per)]
+        chosen = sorted(cand, key=lambda e: (-float(c[t, e]), e))[:top]
+        total = sum(float(s[t, e]) for e in chosen) + 1e-20
+        for e in chosen:
+            out[t, e] = float(s[t, e]) / total * scale
+    if shared_gate:
+        out[:, n_experts] = torch.sigmoid(z[:, n_experts].double()).float()
+    return out
+
+
+def moe_expert_act(gu, wts, n_experts, ff, limit, shared_ff, shared_limit, alpha, out):
+    T = gu.shape[0]
+    v = gu.double()
+    E = n_experts
+    g = v[:, :2 * E * ff].view(T, E, 2, ff)
+    gate, up = torch.clamp(g[:, :, 0], max=limit), torch.clamp(g[:, :, 1], min=-limit, max=limit)
+    a = gate * torch.sigmoid(alpha * gate) * (up + 1.0) * wts[:, :E].double()[:, :, None]
+    out[:, :E * ff] = a.reshape(T, E * ff).to(out.dtype)
+    if shared_ff:
+        sg = v[:, 2 * E * ff:].view(T, 2, shared_ff)
+        gate, up = torch.clamp(sg[:, 0], max=shared_limit), torch.clamp(sg[:, 1], min=-shared_limit, max=shared_limit)
+        out[:, E * ff:] = (gate * torch.sigmoid(alpha * gate) * (up + 1.0) * wts[:, E:E + 1].double()).to(out.dtype)
     return out
