@@ -6,7 +6,7 @@
 //   o_h[i]        = sum_j p_h[i, j] v_kv(h)[j]
 //
 // A key j is seen by the query at position i when j <= i and, with a block size B > 0, floor(j / B) ==
-// floor(i / B).  sink is 1 (a key of score 0 without a value) or 0.  Keys have `d` features and values `dv`,
+// floor(i / B), and, with a window W > 0, i - j < W.  sink is 1 (a key of score 0 without a value) or 0.  Keys have `d` features and values `dv`,
 // which need not be equal.  Values may be stored rotated by their own position (pairs m, m + dv/2, angle
 // j * inv_v[m]); the head's output is then turned back by the query's position.
 //
@@ -105,6 +105,7 @@ struct TalkShape {
     int H, G, d, dv;
     int block;          // keys are seen within blocks of this many positions (0: all earlier keys)
     int sink;           // 1: one is added to the softmax's denominator
+    int window;         // keys are seen among the query's last `window` positions (0: no such limit)
     int kt;             // keys per tile (<= 32)
     float scale;
 };
@@ -152,7 +153,8 @@ talk_attention_plain_kernel(const T* __restrict__ q_rows, int q_row_elems, const
         m_s[u] = sh.sink ? 0.f : -CUDART_INF_F;
         l_s[u] = sh.sink ? 1.f : 0.f;
     }
-    const int first = sh.block > 0 ? (pos / sh.block) * sh.block : 0;
+    int first = sh.block > 0 ? (pos / sh.block) * sh.block : 0;
+    if (sh.window > 0) first = max(first, pos - sh.window + 1);
     const int* table = page_table + (size_t)slot * table_stride;
     for (int j0 = first; j0 <= pos; j0 += KT) {
         const int kt = min(KT, pos - j0 + 1);
@@ -272,6 +274,7 @@ constexpr int TALK_MMA_WARPS = 16, TALK_MMA_THREADS = TALK_MMA_WARPS * 32;
 
 struct TalkMmaShape {
     int H, G, d, dv, block, sink;
+    int window;         // keys are seen among the query's last `window` positions (0: no such limit)
     int qr;             // rows of the operands kept (16 or 8; 1 in a decode step, whose CTAs own one row each)
     int rows;           // rows of the step a CTA owns (qr, or 1 in a decode step)
     int bn;             // keys per tile (16, 32, 64)
@@ -367,6 +370,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
         const int slot = slot_s[a];
         if (slot >= 0) {
             int first = sh.block > 0 ? (pos_s[a] / sh.block) * sh.block : 0, last = pos_s[b - 1];
+            if (sh.window > 0) first = max(first, pos_s[a] - sh.window + 1);       // the run's first row reaches back farthest
             if (split) {
                 first += ((int)blockIdx.y / sh.hg) * sh.chunk;
                 last = min(last, first + sh.chunk - 1);
@@ -438,6 +442,7 @@ talk_attention_mma_kernel(const bf16* __restrict__ q_rows, int q_row_elems, cons
                     const int r = pair >> bn_log2, c = pair & (BN - 1), j = j0 + c;
                     bool seen = r >= a && r < b && j <= pos_s[r];
                     if (seen && sh.block > 0) seen = j >= (pos_s[r] / sh.block) * sh.block;
+                    if (seen && sh.window > 0) seen = j > pos_s[r] - sh.window;
                     float* at = raw_s + (size_t)r * L.rs + c;
                     const size_t hs = (size_t)QR * L.rs;
                     if (!seen) {
@@ -726,19 +731,20 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
                                       const int* page_table, int table_stride, const float* talk, const float* inv_v,
                                       void* out, int T, int H, int G, int d, int dv, float scale, int block, int sink,
                                       int one_row, int max_keys, int n_chunks, float* partial, long long partial_floats,
-                                      cudaStream_t stream) {
+                                      int window, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G) return fail("talk_attention: %d query heads do not divide over %d key/value heads", H, G);
     if (d <= 0 || dv <= 0) return fail("talk_attention: key size %d, value size %d", d, dv);
     if (inv_v != nullptr && (dv & 1)) return fail("talk_attention: rotated values need an even size, found %d", dv);
     if (q_row_elems < H * d) return fail("talk_attention: query rows of %d elements are too short", q_row_elems);
     if (block < 0) return fail("talk_attention: block size %d", block);
+    if (window < 0) return fail("talk_attention: window %d", window);
     if (dtype == JANIS_BF16 && talk_kernel_choice == 1 && q_row_elems % 8 == 0 &&
         (((uintptr_t)q_rows | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0) {
         size_t mma_bytes = 0;
         TalkMmaShape ms = talk_mma_shape(H, G, d, dv, one_row, &mma_bytes);
         if (ms.qr) {
-            ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale;
+            ms.H = H; ms.G = G; ms.d = d; ms.dv = dv; ms.block = block; ms.sink = sink ? 1 : 0; ms.scale = scale; ms.window = window;
             if (one_row && n_chunks > 1 && max_keys > 0 && partial != nullptr) {
                 // a decode row's keys over n_chunks CTAs, each a whole number of tiles
                 if (partial_floats < (long long)T * n_chunks * H * (dv + 2))
@@ -758,7 +764,7 @@ JANIS_EXPORT int janis_talk_attention(const void* q_rows, int dtype, int q_row_e
     }
     size_t bytes = 0;
     TalkShape sh;
-    sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale;
+    sh.H = H; sh.G = G; sh.d = d; sh.dv = dv; sh.block = block; sh.sink = sink ? 1 : 0; sh.scale = scale; sh.window = window;
     sh.kt = talk_plain_tile(H, G, d, dv, &bytes);
     if (sh.kt == 0) return fail("talk_attention: heads of these sizes do not fit shared memory (%d x %d, %d x %d)", H, d, G, dv);
     const dim3 grid(T), block_dim(256);

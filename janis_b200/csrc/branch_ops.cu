@@ -1,0 +1,267 @@
+// Rows of the residual stream and of a layer's branches: the Dynamic Tanh norm, the norm-and-accumulate of branches
+// that run side by side, and a sigmoid gate on the heads of an attention.  All arithmetic is float.
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace janis {
+
+// h[r] += res[r] (when res is given: the float residual sum, in place), then
+// y[r] = tanh(alpha * h[src]) * w + b with src = rows[r] (or r): no statistics of the row are taken.
+template <typename TR, typename TO>
+__global__ void __launch_bounds__(256)
+dyt_norm_kernel(float* __restrict__ h, const TR* __restrict__ res, const int* __restrict__ rows, float alpha,
+                const float* __restrict__ w, const float* __restrict__ b, TO* __restrict__ y, int H) {
+    const int r = blockIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int src = rows != nullptr ? rows[r] : r;
+    float* hr = h + (size_t)src * H;
+    TO* yr = y + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = hr[i];
+        if (res != nullptr) {
+            v += to_float(res[(size_t)r * H + i]);
+            hr[i] = v;
+        }
+        yr[i] = from_float<TO>(fmaf(tanhf(alpha * v), w[i], b[i]));
+    }
+}
+
+// acc[r] = (first ? 0 : acc[r]) + share * x[r] / sqrt(mean(x[r]^2) + eps) * w
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_accumulate_kernel(const T* __restrict__ x, const float* __restrict__ w, float eps, float share,
+                          float* __restrict__ acc, int first, int H) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const T* xr = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = share / sqrtf(ss / (float)H + eps);
+    float* ar = acc + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = to_float(xr[i]) * inv * w[i];
+        ar[i] = first ? v : ar[i] + v;
+    }
+}
+
+// x[t, c] *= sigmoid(rows[t, g_off + c])
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ rows, int row_elems, int g_off, int width, size_t n) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / width;
+        const int c = (int)(i % width);
+        const float g = to_float(rows[t * row_elems + g_off + c]);
+        x[i] = from_float<T>(to_float(x[i]) / (1.0f + expf(-g)));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Mixture of experts: the router and the experts' activation.
+//
+// router, a warp per token over E logits z (float):  s = sigmoid(z), c = s + correction;  experts form n_groups equal
+// groups of neighbours, a group's score is the sum of its two largest c, the best `keep` groups stay (ties: the
+// lower index); among their experts the `top` of largest c are chosen (ties: the lower index); the chosen get
+// w_e = s_e / (sum of the chosen s + 1e-20) * scale, every other expert 0.  With a shared gate, column E of z is
+// its logit and column E of the output its sigmoid.
+// ---------------------------------------------------------------------------
+constexpr int ROUTE_WARPS = 4;
+
+__device__ __forceinline__ void warp_argmax(float& v, int& at) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > v || (ov == v && oa < at)) { v = ov; at = oa; }
+    }
+}
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const float* __restrict__ z, const float* __restrict__ correction, int T, int E, int n_groups, int keep,
+                 int top, float scale, int shared_gate, float* __restrict__ out) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, t = blockIdx.x * ROUTE_WARPS + warp;
+    float* s = smem + (size_t)warp * (3 * E);        // scores
+    float* c = s + E;                                // choice scores (minus infinity once out of the running)
+    float* gs = c + E;                               // group scores
+    grid_dependents_launch();
+    grid_dependency_wait();
+    if (t >= T) return;
+    const int cols = E + (shared_gate ? 1 : 0), per = E / n_groups;
+    const float* zr = z + (size_t)t * cols;
+    float* o = out + (size_t)t * cols;
+    for (int e = lane; e < E; e += 32) {
+        const float v = 1.0f / (1.0f + expf(-zr[e]));
+        s[e] = v;
+        c[e] = v + correction[e];
+        o[e] = 0.f;
+    }
+    if (shared_gate && lane == 0) o[E] = 1.0f / (1.0f + expf(-zr[E]));
+    __syncwarp();
+    if (n_groups > 1 && keep < n_groups) {
+        for (int g = lane; g < n_groups; g += 32) {
+            float a = -CUDART_INF_F, b = -CUDART_INF_F;      // the two largest
+            for (int e = g * per; e < (g + 1) * per; ++e) {
+                const float v = c[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            gs[g] = per > 1 ? a + b : a;
+        }
+        __syncwarp();
+        // the kept groups get +inf as a mark; the others' experts leave the running
+        for (int k = 0; k < keep; ++k) {
+            float v = -CUDART_INF_F;
+            int at = 0x7fffffff;
+            for (int g = lane; g < n_groups; g += 32) {
+                const float gv = gs[g];
+                if (gv != CUDART_INF_F && (gv > v || (gv == v && g < at))) { v = gv; at = g; }
+            }
+            warp_argmax(v, at);
+            __syncwarp();
+            if (lane == 0 && at < n_groups) gs[at] = CUDART_INF_F;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != CUDART_INF_F) c[e] = -CUDART_INF_F;
+        __syncwarp();
+    }
+    float total = 0.f;
+    for (int k = 0; k < top; ++k) {
+        float v = -CUDART_INF_F;
+        int at = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float cv = c[e];
+            if (cv > v || (cv == v && e < at)) { v = cv; at = e; }
+        }
+        warp_argmax(v, at);
+        __syncwarp();
+        if (at >= E) break;                          // nothing left in the running
+        total += s[at];
+        if (lane == 0) {
+            c[at] = -CUDART_INF_F;
+            o[at] = -1.f;                            // marked; weighed below
+        }
+        __syncwarp();
+    }
+    const float f = scale / (total + 1e-20f);
+    for (int e = lane; e < E; e += 32)
+        if (o[e] < 0.f) o[e] = s[e] * f;
+}
+
+// a[t, col] = w[t, e] * g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, -limit, limit), over the
+// columns of all experts side by side (expert e: `ff` columns; then the shared expert's `shared_ff`); in gu an
+// expert's gate columns are followed by its up columns.  Experts of weight 0 give exact zeros.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_expert_act_kernel(const T* __restrict__ gu, const float* __restrict__ wts, int E, int ff, float limit, int shared_ff,
+                      float shared_limit, float alpha, T* __restrict__ out, size_t n) {
+    const int total = E * ff + shared_ff, wcols = E + (shared_ff ? 1 : 0);
+    grid_dependents_launch();
+    grid_dependency_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / total;
+        const int col = (int)(i % total);
+        int e, j, width;
+        float lim;
+        size_t base;
+        if (col < E * ff) { e = col / ff; j = col % ff; width = ff; lim = limit; base = (size_t)2 * e * ff; }
+        else { e = E; j = col - E * ff; width = shared_ff; lim = shared_limit; base = (size_t)2 * E * ff; }
+        const float w = wts[t * wcols + e];
+        float a = 0.f;
+        if (w != 0.f) {
+            const T* row = gu + t * (size_t)(2 * total) + base;
+            const float g = fminf(to_float(row[j]), lim);
+            const float u = fminf(fmaxf(to_float(row[width + j]), -lim), lim);
+            a = w * (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+        }
+        out[i] = from_float<T>(a);
+    }
+}
+
+}  // namespace janis
+
+using namespace janis;
+
+static inline unsigned flat_grid(size_t n) {
+    const size_t want = (n + 255) / 256;
+    return (unsigned)(want < 148 * 16 ? (want ? want : 1) : 148 * 16);
+}
+
+JANIS_EXPORT int janis_dyt_norm(float* h, const void* res, int res_dtype, const int* rows, float alpha, const float* w,
+                                const float* b, void* y, int y_dtype, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    if (res != nullptr && rows != nullptr) return fail("dyt_norm: a residual is added to all rows, not to chosen ones");
+    const dim3 grid(R), block(H >= 1024 ? 256 : 128);
+#define JANIS_DYT(TR, TO)                                                                                              \
+    return launch_kernel("dyt_norm", dyt_norm_kernel<TR, TO>, grid, block, 0, stream, 1, h, (const TR*)res, rows, alpha, w, \
+                         b, (TO*)y, H);
+    const int rd = res != nullptr ? res_dtype : JANIS_F32;
+    if (rd == JANIS_F32 && y_dtype == JANIS_F32) { JANIS_DYT(float, float) }
+    if (rd == JANIS_F32 && y_dtype == JANIS_BF16) { JANIS_DYT(float, bf16) }
+    if (rd == JANIS_BF16 && y_dtype == JANIS_F32) { JANIS_DYT(bf16, float) }
+    if (rd == JANIS_BF16 && y_dtype == JANIS_BF16) { JANIS_DYT(bf16, bf16) }
+#undef JANIS_DYT
+    return fail("dyt_norm: unknown dtypes %d, %d", res_dtype, y_dtype);
+}
+
+JANIS_EXPORT int janis_rmsnorm_accumulate(const void* x, int dtype, const float* w, float eps, float share, float* acc,
+                                          int first, int R, int H, cudaStream_t stream) {
+    if (R <= 0) return 0;
+    const dim3 grid(R), block(H >= 1024 ? 256 : 128);
+    if (dtype == JANIS_F32)
+        return launch_kernel("rmsnorm_accumulate", rmsnorm_accumulate_kernel<float>, grid, block, 0, stream, 1,
+                             (const float*)x, w, eps, share, acc, first, H);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("rmsnorm_accumulate", rmsnorm_accumulate_kernel<bf16>, grid, block, 0, stream, 1,
+                             (const bf16*)x, w, eps, share, acc, first, H);
+    return fail("rmsnorm_accumulate: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_sigmoid_gate(void* x, const void* rows, int dtype, int row_elems, int g_off, int T, int width,
+                                    cudaStream_t stream) {
+    if (T <= 0 || width <= 0) return 0;
+    if (g_off < 0 || g_off + width > row_elems) return fail("sigmoid_gate: %d gates at %d do not fit rows of %d", width, g_off, row_elems);
+    const size_t n = (size_t)T * width;
+    if (dtype == JANIS_F32)
+        return launch_kernel("sigmoid_gate", sigmoid_gate_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, 1, (float*)x,
+                             (const float*)rows, row_elems, g_off, width, n);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("sigmoid_gate", sigmoid_gate_kernel<bf16>, dim3(flat_grid(n)), dim3(256), 0, stream, 1, (bf16*)x,
+                             (const bf16*)rows, row_elems, g_off, width, n);
+    return fail("sigmoid_gate: unknown dtype %d", dtype);
+}
+
+JANIS_EXPORT int janis_moe_route(const float* z, const float* correction, int T, int E, int n_groups, int keep, int top,
+                                 float scale, int shared_gate, float* out, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || E > 1024) return fail("moe_route: %d experts (up to 1024 are taken)", E);
+    if (n_groups <= 0 || E % n_groups || keep <= 0 || keep > n_groups || top <= 0 || top > keep * (E / n_groups))
+        return fail("moe_route: %d experts in %d groups, %d kept, %d chosen", E, n_groups, keep, top);
+    const size_t bytes = (size_t)ROUTE_WARPS * 3 * E * sizeof(float);
+    return launch_kernel("moe_route", moe_route_kernel, dim3((T + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
+                         bytes, stream, 1, z, correction, T, E, n_groups, keep, top, scale, shared_gate, out);
+}
+
+JANIS_EXPORT int janis_moe_expert_act(const void* gu, int dtype, const float* wts, int E, int ff, float limit, int shared_ff,
+                                      float shared_limit, float alpha, void* out, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const size_t n = (size_t)T * ((size_t)E * ff + shared_ff);
+    if (dtype == JANIS_F32)
+        return launch_kernel("moe_expert_act", moe_expert_act_kernel<float>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
+                             (const float*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (float*)out, n);
+    if (dtype == JANIS_BF16)
+        return launch_kernel("moe_expert_act", moe_expert_act_kernel<bf16>, dim3(flat_grid(n)), dim3(256), 0, stream, 1,
+                             (const bf16*)gu, wts, E, ff, limit, shared_ff, shared_limit, alpha, (bf16*)out, n);
+    return fail("moe_expert_act: unknown dtype %d", dtype);
+}

@@ -4,7 +4,8 @@ There are three kinds of library: `core` (norms, embedding, rotary encoding and
 cache write, the 32-bit product, the skinny bfloat16 product, sampling), one
 `attention` library per head size, compiled with that size as a constant, and
 `mixers` (attention whose heads are mixed before the softmax, with values of a
-size of their own; gated linear attention), whose sizes are run-time numbers.  A
+size of their own; gated linear attention; the state-space scans with their
+convolution; Dynamic Tanh, branch and expert-routing kernels), whose sizes are run-time numbers.  A
 library is compiled the first time it is asked for, so a process compiles what
 its model needs and nothing else; the file name carries a hash of the sources
 and flags, so a stale library is never loaded.  The kernels are plain C entry
@@ -35,7 +36,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompil
 
 CORE_SOURCES = ["elementwise.cu", "gemm_f32.cu", "gemv_bf16.cu", "gemm_tc05.cu", "sampling.cu"]
 ATTENTION_SOURCES = ["attention.cu", "attention_prefill_mma.cu", "attention_prefill_tc05.cu", "attention_no_alloc.cu"]
-MIXER_SOURCES = ["attention_talk.cu", "linear_attention.cu"]
+MIXER_SOURCES = ["attention_talk.cu", "linear_attention.cu", "state_space.cu", "branch_ops.cu"]
 HEADERS = ["common.cuh", "attention_no_alloc.h", "attention_prefill_tiles.cuh"]
 
 

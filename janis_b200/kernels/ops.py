@@ -138,11 +138,19 @@ def mixers():
         lib = build.mixers_library()
         P, I, F = c_void_p, c_int, c_float
         lib.janis_qkv_rotate_store.argtypes = [P, I, I, P, P, P, P, I, P, I, I, I, I, I, I, P, P, P, I, P]
-        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, P]
+        lib.janis_talk_attention.argtypes = [P, I, I, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, I, I, I, I, I, P, c_longlong, I, P]
         lib.janis_talk_attention_set_kernel.argtypes = [I]
         lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
+        lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, P, P]
+        lib.janis_selective_scan.argtypes = [P, I, I, I, P, I, I, P, P, I, P, I, I, I, P, P, I, I, P, P, P, P, I, P, P, I, I, I, I, P]
+        lib.janis_gate_group_norm.argtypes = [P, P, I, I, I, P, F, I, P, I, I, P]
+        lib.janis_dyt_norm.argtypes = [P, P, I, P, F, P, P, P, I, I, I, P]
+        lib.janis_rmsnorm_accumulate.argtypes = [P, I, P, F, F, P, I, I, I, P]
+        lib.janis_sigmoid_gate.argtypes = [P, P, I, I, I, I, I, P]
+        lib.janis_moe_route.argtypes = [P, P, I, I, I, I, I, F, I, P, P]
+        lib.janis_moe_expert_act.argtypes = [P, I, P, I, I, F, I, F, F, P, I, P]
         lib.janis_mixers_set_overlap.argtypes = [I]
         lib.janis_mixers_set_overlap.restype = None
         lib.janis_mixers_set_overlap(1 if _overlap else 0)
@@ -790,11 +798,11 @@ def qkv_rotate_store(rows, tok_pos, tok_seq, seq_slot, inv_qk, rot: int, inv_v, 
 
 def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table, talk, inv_v, out, H: int, G: int,
                    d: int, dv: int, scale: float, block: int = 0, sink: bool = False, one_row: bool = False,
-                   max_keys: int = 0, n_chunks: int = 1, scratch=None):
+                   max_keys: int = 0, n_chunks: int = 1, scratch=None, window: int = 0):
     """Causal attention of every token of the step over its sequence's cache line (which already holds the step's
     own keys and values).  The scaled scores of the H query heads are mixed by talk [H, H] float32 (None: left
     alone) before the softmax; with block > 0 a key is seen only inside the query's block of that many positions;
-    with sink, 1 is added to the softmax's denominator; with inv_v each head's output is turned back by the query's
+    with window > 0 only among the query's last `window` positions (its own included); with sink, 1 is added to the softmax's denominator; with inv_v each head's output is turned back by the query's
     position (the cached values were rotated by theirs).  q_rows [T, >= H d], out [T, H dv].
     bfloat16 with d a multiple of 16, dv a multiple of 8 and up to 32 heads runs on the tensor cores (a CTA per 16
     or 8 rows of the step; one_row=True, for decode steps, gives every row a CTA of its own); everything else
@@ -819,7 +827,7 @@ def talk_attention(q_rows, tok_pos, tok_seq, seq_slot, kpool, vpool, page_table,
         _t(inv_v, "inv_v", torch.float32, (dv // 2,)) if inv_v is not None else None, out.data_ptr(), T, H, G, d, dv,
         float(scale), int(block), 1 if sink else 0, 1 if one_row else 0, int(max_keys), int(n_chunks),
         _t(scratch, "scratch", torch.float32) if scratch is not None else None,
-        scratch.numel() if scratch is not None else 0, _stream()),
+        scratch.numel() if scratch is not None else 0, int(window), _stream()),
         kernels=2 if (one_row and n_chunks > 1 and scratch is not None and q_rows.dtype == torch.bfloat16) else 1)
     return out
 
@@ -875,6 +883,151 @@ def head_norm_gate(o, rows, g_off: int, weight, eps: float, out, H: int, dv: int
     _check(lib, lib.janis_head_norm_gate(o.data_ptr(), rows.data_ptr() if rows is not None else None, _DT[out.dtype],
                                          rows.shape[1] if rows is not None else 0, g_off, weight.data_ptr(), float(eps),
                                          out.data_ptr(), T, H, dv, _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Dynamic Tanh, state-space mixers, branches side by side, mixture of experts
+# ---------------------------------------------------------------------------
+
+def dyt_norm(h, res, alpha: float, weight, bias, out, rows=None):
+    """h += res (when res is given: the float32 residual sum, in place), then out[r] = tanh(alpha h[rows[r] or r]) *
+    weight + bias.  h float32 [T, H]; res [T, H] float32 or bfloat16 (not together with rows); weight, bias float32."""
+    H = h.shape[-1]
+    R = out.shape[0]
+    if rows is None and h.shape[0] != R:
+        raise KernelError(f"dyt_norm: {h.shape[0]} input rows for {R} output rows")
+    lib = mixers()
+    _check(lib, lib.janis_dyt_norm(_t(h, "h", torch.float32, (None, H)),
+                                   _t(res, "res", _FLOATS, (R, H)) if res is not None else None,
+                                   _DT[res.dtype] if res is not None else 0,
+                                   _t(rows, "rows", torch.int32, (R,)) if rows is not None else None, float(alpha),
+                                   _t(weight, "weight", torch.float32, (H,)), _t(bias, "bias", torch.float32, (H,)),
+                                   _t(out, "out", _FLOATS, (R, H)), _DT[out.dtype], R, H, _stream()))
+    return out
+
+
+def causal_conv_silu(rows, col_off: int, channels: int, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
+                     seq_end, n_seq: int, out):
+    """out[t, c] = silu(bias[c] + sum_j weight[c, K-1-j] x[t-j, c]) over the channels rows[:, col_off : col_off +
+    channels] of each sequence's tokens; inputs before the step come from state float32 [slots, max(K-1, 1), channels]
+    (the last K-1 inputs of each slot), which a second kernel then brings up to date.  Sequences without a slot
+    start from zeros and store nothing.  weight float32 [channels, K], bias float32 [channels]."""
+    T, width = rows.shape
+    K = weight.shape[1]
+    _t(rows, "rows", _FLOATS, (T, None))
+    _t(state, "state", torch.float32, (None, max(K - 1, 1), channels))
+    for name, tab, n in (("tok_seq", tok_seq, T), ("seq_slot", seq_slot, n_seq), ("seq_first_row", seq_first_row, n_seq),
+                         ("seq_start", seq_start, n_seq), ("seq_end", seq_end, n_seq)):
+        _t(tab, name, torch.int32)
+        if tab.numel() < n:
+            raise KernelError(f"causal_conv_silu: {name} shorter than the step")
+    lib = mixers()
+    _check(lib, lib.janis_causal_conv_silu(rows.data_ptr(), _DT[rows.dtype], width, int(col_off), int(channels), K,
+                                           _t(weight, "weight", torch.float32, (channels, K)),
+                                           _t(bias, "bias", torch.float32, (channels,)), state.data_ptr(),
+                                           tok_seq.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(),
+                                           seq_start.data_ptr(), seq_end.data_ptr(), T, n_seq,
+                                           _t(out, "out", rows.dtype, (T, channels)), _stream()), kernels=2 if K > 1 else 1)
+    return out
+
+
+def selective_scan(u, u_off: int, dt, dt_off: int, dt_bias, A, a_per_state: bool, bc, b_off: int, c_off: int, D, z,
+                   z_off: int, seq_slot, seq_first_row, seq_start, seq_end, n_seq: int, state, out, C: int, N: int,
+                   ch_per_head: int, ch_per_group: int):
+    """The recurrence S[c, n] <- exp(delta A) S[c, n] + delta u[c] B[n], o[c] = sum_n S[c, n] C[n] + D u[c] over the
+    tokens each sequence brings, in order, with delta = softplus(dt + dt_bias).  u [T, *] holds the channels at
+    u_off; dt [T, *] one step size per head (c // ch_per_head) at dt_off; bc [T, *] holds B at b_off and C at c_off,
+    N numbers per group (c // ch_per_group); A float32 is [heads, N] (a_per_state) or [heads]; dt_bias, D float32
+    [heads].  With z ([T, *], the gate's channels at z_off) out [T, C] takes o * silu(z) in the activations' type;
+    without, out is float32 o.  state float32 [slots, C, N] is read and written back for slots >= 0."""
+    T = u.shape[0]
+    heads = C // ch_per_head
+    dtype = u.dtype
+    for name, x in (("u", u), ("dt", dt), ("bc", bc)) + ((("z", z),) if z is not None else ()):
+        _t(x, name, dtype, (T, None))
+    _t(dt_bias, "dt_bias", torch.float32, (heads,))
+    _t(A, "A", torch.float32, (heads, N) if a_per_state else (heads,))
+    _t(D, "D", torch.float32, (heads,))
+    _t(state, "state", torch.float32, (None, C, N))
+    _t(out, "out", dtype if z is not None else torch.float32, (T, C))
+    if u_off + C > u.shape[1] or dt_off + heads > dt.shape[1] or max(b_off, c_off) + (C // ch_per_group) * N > bc.shape[1] \
+            or (z is not None and z_off + C > z.shape[1]):
+        raise KernelError("selective_scan: a column range lies outside its rows")
+    for name, tab in (("seq_slot", seq_slot), ("seq_first_row", seq_first_row), ("seq_start", seq_start), ("seq_end", seq_end)):
+        _t(tab, name, torch.int32)
+        if tab.numel() < n_seq:
+            raise KernelError(f"selective_scan: {name} shorter than the step's sequences")
+    lib = mixers()
+    _check(lib, lib.janis_selective_scan(
+        u.data_ptr(), _DT[dtype], u.shape[1], int(u_off), dt.data_ptr(), dt.shape[1], int(dt_off), dt_bias.data_ptr(),
+        A.data_ptr(), 1 if a_per_state else 0, bc.data_ptr(), bc.shape[1], int(b_off), int(c_off), D.data_ptr(),
+        z.data_ptr() if z is not None else None, z.shape[1] if z is not None else 0, int(z_off), seq_slot.data_ptr(),
+        seq_first_row.data_ptr(), seq_start.data_ptr(), seq_end.data_ptr(), n_seq, state.data_ptr(), out.data_ptr(),
+        C, N, int(ch_per_head), int(ch_per_group), _stream()))
+    return out
+
+
+def gate_group_norm(o, rows, z_off: int, weight, eps: float, n_groups: int, out):
+    """out = rms(o * silu(z)) * weight, the root mean square taken over each of n_groups equal parts of a row;
+    o float32 [T, C], z = rows[:, z_off : z_off + C], weight float32 [C]."""
+    T, C = o.shape
+    _t(o, "o", torch.float32, (T, C))
+    _t(rows, "rows", out.dtype, (T, None))
+    if z_off + C > rows.shape[1]:
+        raise KernelError("gate_group_norm: the gate lies outside its rows")
+    lib = mixers()
+    _check(lib, lib.janis_gate_group_norm(o.data_ptr(), rows.data_ptr(), _DT[out.dtype], rows.shape[1], int(z_off),
+                                          _t(weight, "weight", torch.float32, (C,)), float(eps), int(n_groups),
+                                          _t(out, "out", _FLOATS, (T, C)), T, C, _stream()))
+    return out
+
+
+def rmsnorm_accumulate(x, weight, eps: float, scale: float, acc, first: bool = False):
+    """acc = (0 if first else acc) + scale * x / sqrt(mean(x^2) + eps) * weight; x [T, H], acc float32 [T, H]."""
+    T, H = x.shape
+    lib = mixers()
+    _check(lib, lib.janis_rmsnorm_accumulate(_t(x, "x", _FLOATS, (T, H)), _DT[x.dtype], _t(weight, "weight", torch.float32, (H,)),
+                                             float(eps), float(scale), _t(acc, "acc", torch.float32, (T, H)),
+                                             1 if first else 0, T, H, _stream()))
+    return acc
+
+
+def sigmoid_gate(x, rows, g_off: int):
+    """x[t, c] *= sigmoid(rows[t, g_off + c]) in place; x [T, n], rows [T, >= g_off + n] of x's dtype."""
+    T, n = x.shape
+    lib = mixers()
+    _check(lib, lib.janis_sigmoid_gate(_t(x, "x", _FLOATS, (T, n)), _t(rows, "rows", x.dtype, (T, None)), _DT[x.dtype],
+                                       rows.shape[1], int(g_off), T, n, _stream()))
+    return x
+
+
+def moe_route(z, correction, n_experts: int, group_count: int, group_keep: int, top: int, scale: float,
+              shared_gate: bool, out):
+    """The router's weights per token and expert, 0 for experts that were not chosen: s = sigmoid(z), choice scores
+    s + correction, the best group_keep of group_count groups (by the sum of a group's two largest choice scores), the
+    `top` largest choice scores among their experts, w = s / (sum of the chosen s + 1e-20) * scale.  With
+    shared_gate, column n_experts of z is a gate's logit and column n_experts of out its sigmoid.  z, out float32."""
+    T = z.shape[0]
+    cols = n_experts + (1 if shared_gate else 0)
+    lib = mixers()
+    _check(lib, lib.janis_moe_route(_t(z, "z", torch.float32, (T, cols)), _t(correction, "correction", torch.float32, (n_experts,)),
+                                    T, n_experts, int(group_count), int(group_keep), int(top), float(scale),
+                                    1 if shared_gate else 0, _t(out, "out", torch.float32, (T, cols)), _stream()))
+    return out
+
+
+def moe_expert_act(gu, wts, n_experts: int, ff: int, limit: float, shared_ff: int, shared_limit: float, alpha: float, out):
+    """out[t, e * ff + j] = wts[t, e] * g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit,
+    limit); gu [T, 2 (E ff + shared_ff)] holds each expert's ff gate columns followed by its ff up columns, the
+    shared expert (weight wts[t, E], its own limit) last; out [T, E ff + shared_ff]."""
+    T = gu.shape[0]
+    total = n_experts * ff + shared_ff
+    lib = mixers()
+    _check(lib, lib.janis_moe_expert_act(_t(gu, "gu", _FLOATS, (T, 2 * total)), _DT[gu.dtype],
+                                         _t(wts, "wts", torch.float32, (T, n_experts + (1 if shared_ff else 0))),
+                                         n_experts, ff, float(limit), int(shared_ff), float(shared_limit), float(alpha),
+                                         _t(out, "out", gu.dtype, (T, total)), T, _stream()))
     return out
 
 
