@@ -22,6 +22,7 @@ bfloat16 matrix peak.
 from __future__ import annotations
 
 import argparse
+import copy
 import json
 import os
 import subprocess
@@ -497,8 +498,44 @@ def sigalorn_like(gemma: dict, layers: int) -> dict:
             "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": out}
 
 
-_TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_norm_gate", "bias_act"),
-          "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act")}
+def nosolix_like(gemma: dict, layers: int) -> dict:
+    """A Nosolix configuration with the layer sizes of a Gemma2 one: the same width, heads, head size (for keys and
+    values), feed-forward width and vocabulary; layers alternate "parallel" (attention over Gemma2's window beside a
+    state-space-duality mixer of twice the width in heads of 64 channels with 128 states) and "mamba1" (twice the
+    width in channels, 16 states, step sizes through a rank of a sixteenth of the width); feed-forwards alternate
+    dense and a mixture of 16 experts of a quarter of the dense width, 4 chosen from the best 2 of 4 groups, with a
+    shared expert of that width: as many active feed-forward weights a token as the dense layer."""
+    hd, W, ff = int(gemma["head_dim"]), int(gemma["hidden_size"]), int(gemma["intermediate_size"])
+    left = {"heads": gemma["num_attention_heads"], "kv_heads": gemma["num_key_value_heads"], "dim": hd, "vdim": hd,
+            "scale": hd ** -0.5, "mask": {"size": int(gemma.get("sliding_window", 4096))},
+            "rot": {"base": 10000.0, "dims": hd, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": 2 * W // 64, "vdim": 64, "state": 128, "groups": 1, "norm_groups": 1, "conv": 4}
+    scan = {"inner": 2 * W, "state": 16, "dt_rank": max(8, W // 16), "conv": 4}
+    e_ff = max(8, ff // 4 // 8 * 8)
+    moe = {"kind": "moe", "expert": {"ff": e_ff, "limit": 7.0}, "shared": {"ff": e_ff, "limit": 7.0},
+           "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        mixer = {"left": dict(left), "right": dict(right)} if i % 2 == 0 else dict(scan)
+        mlp = {"kind": "dense", "ff": ff} if i % 4 < 2 else copy.deepcopy(moe)
+        out.append({"type": "parallel" if i % 2 == 0 else "mamba1", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Nosolix", "vocab": gemma["vocab_size"], "width": W, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": out}
+
+
+_TIMED = {"sigalorn": ("talk_attention", "qkv_rotate_store", "gla_scan", "head_norm_gate", "bias_act", "add_rmsnorm", "rmsnorm"),
+          "gemma2": ("attn_prefill", "attn_decode", "rope_store", "gemv_rope_store", "gated_act"),
+          "nosolix": ("talk_attention", "qkv_rotate_store", "selective_scan", "causal_conv_silu", "gate_group_norm",
+                      "moe_route", "moe_expert_act", "dyt_norm", "rmsnorm_accumulate", "sigmoid_gate", "bias_act")}
+
+
+def _leaf_mixers(mixer):
+    branches = getattr(mixer, "branches", None)
+    if not branches:
+        yield mixer
+        return
+    for m in branches.values():
+        yield from _leaf_mixers(m)
 
 
 def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: int, context: int, steps: int,
@@ -539,27 +576,36 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
     att_flops = gla_flops = 0.0
     kv_bytes = state_bytes = 0
     for call in model.schedule:
-        mixer = model.blocks[call.layer].mixer
-        for need in mixer.cache_needs().values():
-            if isinstance(need, KVNeed):
-                att_flops += mixer.prompt_flops(prefill_tokens)
-                seen = min(context, need.window) if need.window else context
-                seen = min(seen, (context - 1) % mixer.block + 1) if getattr(mixer, "block", 0) else seen
-                kv_bytes += batch * seen * need.n_kv_heads * (need.head_dim + need.value_dim) * 2
-            elif isinstance(need, StateNeed):
-                gla_flops += mixer.prompt_flops(prefill_tokens)
-                state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
-    att_name = "talk_attention" if kind == "sigalorn" else "attn_prefill"
-    dec_name = "talk_attention" if kind == "sigalorn" else "attn_decode"
+        for mixer in _leaf_mixers(model.blocks[call.layer].mixer):
+            for name, need in mixer.cache_needs().items():
+                if isinstance(need, KVNeed):
+                    att_flops += mixer.prompt_flops(prefill_tokens)
+                    seen = min(context, need.window) if need.window else context
+                    seen = min(seen, (context - 1) % mixer.block + 1) if getattr(mixer, "block", 0) else seen
+                    seen = min(seen, mixer.window) if getattr(mixer, "window", 0) else seen
+                    kv_bytes += batch * seen * need.n_kv_heads * (need.head_dim + need.value_dim) * 2
+                elif isinstance(need, StateNeed) and name == "state":      # (a convolution's kept inputs are another kernel's)
+                    gla_flops += mixer.prompt_flops(prefill_tokens)
+                    state_bytes += 2 * batch * int(np.prod(need.shape)) * 4
+    att_name = "attn_prefill" if kind == "gemma2" else "talk_attention"
+    dec_name = "attn_decode" if kind == "gemma2" else "talk_attention"
+    scan_name = "selective_scan" if kind == "nosolix" else "gla_scan"
     roof = {}
     if kernels["prefill_us"].get(att_name):
         roof["attention_prefill_frac_of_bf16_peak"] = round(att_flops / (kernels["prefill_us"][att_name] * 1e-6) / (pk["bf16_tflops"] * 1e12), 5)
     if kernels["decode_us"].get(dec_name):
         roof["attention_decode_frac_of_copy_bandwidth"] = round(kv_bytes / (kernels["decode_us"][dec_name] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
-    if kernels["prefill_us"].get("gla_scan"):
-        roof["recurrence_prefill_tflops_fp32"] = round(gla_flops / (kernels["prefill_us"]["gla_scan"] * 1e-6) / 1e12, 3)
-    if kernels["decode_us"].get("gla_scan"):
-        roof["recurrence_decode_frac_of_copy_bandwidth"] = round(state_bytes / (kernels["decode_us"]["gla_scan"] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    if kernels["prefill_us"].get(scan_name):
+        roof["recurrence_prefill_tflops_fp32"] = round(gla_flops / (kernels["prefill_us"][scan_name] * 1e-6) / 1e12, 3)
+    if kernels["decode_us"].get(scan_name):
+        roof["recurrence_decode_frac_of_copy_bandwidth"] = round(state_bytes / (kernels["decode_us"][scan_name] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
+    # the elementwise kernels of a step against the bytes of the residual stream they pass over (one float32 read and
+    # write and one activation written per norm): the norms' share, a number to set beside the other design's
+    T = prefill_tokens
+    for nm in ("dyt_norm", "add_rmsnorm"):
+        if kernels["prefill_us"].get(nm):
+            n_norm = sum(2 if getattr(model.blocks[c.layer], "feed_forward", None) is not None else 1 for c in model.schedule)
+            roof[f"{nm}_prefill_frac_of_copy_bandwidth"] = round(n_norm * T * model.hidden * 10 / (kernels["prefill_us"][nm] * 1e-6) / 1e9 / pk["hbm_gbs"], 5)
     out["kernels"] = kernels
     out["kernel_rooflines"] = roof
     eng.close()
@@ -567,16 +613,21 @@ def _measure_design(raw: dict, kind: str, pk: dict, prefill_tokens: int, batch: 
 
 
 def compare(sizes=("gemma2-2b", "gemma2-9b", "gemma2-27b"), layers: int = 4, prefill_tokens: int = 2048, batch: int = 8,
-            context: int = 4096, steps: int = 64, warmup: int = 4) -> dict:
+            context: int = 4096, steps: int = 64, warmup: int = 4, design: str = "sigalorn") -> dict:
     """Sigalorn beside Gemma2 at the layer sizes of the Gemma2 configurations, `layers` layers each, random
     weights: prompt tokens a second, decode tokens a second, and the device time of each design's own kernels in
     one prompt step and one decode step with what fraction of the roofline that is."""
     pk, pk_kind = peaks()
-    rec = {"compare": "sigalorn beside gemma2", "dtype": "bf16", "data": "synthetic", "peaks": pk_kind,
-           "prefill_tokens": prefill_tokens, "batch": batch, "context": context, "steps": steps, "sizes": {}}
+    rec = {"compare": f"{design} beside {'sigalorn' if design == 'nosolix' else 'gemma2'}", "dtype": "bf16", "data": "synthetic",
+           "peaks": pk_kind, "prefill_tokens": prefill_tokens, "batch": batch, "context": context, "steps": steps, "sizes": {}}
     for name in sizes:
         gemma = dict(load_config(name), num_hidden_layers=layers)
         gemma.pop("layer_types", None)
+        if design == "nosolix":      # beside the closest design the library has: recurrent layers between attention over a limited span
+            rec["sizes"][name] = {
+                "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup),
+                "nosolix": _measure_design(nosolix_like(gemma, layers), "nosolix", pk, prefill_tokens, batch, context, steps, warmup)}
+            continue
         rec["sizes"][name] = {
             "gemma2": _measure_design(gemma, "gemma2", pk, prefill_tokens, batch, context, steps, warmup),
             "sigalorn": _measure_design(sigalorn_like(gemma, layers), "sigalorn", pk, prefill_tokens, batch, context, steps, warmup)}
@@ -604,9 +655,10 @@ def main(argv=None) -> int:
                     "instead of sequences that all reach --context")
     ap.add_argument("--profile", choices=["decode", "prefill"], default="",
                     help="open the CUDA profiler range around two timed decode steps, or the last prompt step")
-    ap.add_argument("--compare", choices=["sigalorn"], default="",
-                    help="instead of the benchmark: Sigalorn beside Gemma2 at equal layer sizes (prompt and decode "
-                    "throughput, and each design's own kernels against their rooflines); --config picks one size")
+    ap.add_argument("--compare", choices=["sigalorn", "nosolix"], default="",
+                    help="instead of the benchmark: Sigalorn beside Gemma2, or Nosolix beside Sigalorn, at equal layer "
+                    "sizes (prompt and decode throughput, and each design's own kernels against their rooflines); "
+                    "--config picks one size")
     a = ap.parse_args(argv)
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "the reference is a Go module (no Go toolchain here, "
@@ -619,7 +671,7 @@ def main(argv=None) -> int:
         sizes = ("gemma2-2b", "gemma2-9b", "gemma2-27b") if a.config == "gemma2-2b" and "--config" not in (argv or sys.argv) \
             else ((a.config if a.config.startswith("gemma2-") else "gemma2-" + a.config),)
         print(json.dumps(compare(sizes, a.layers or 4, a.prefill, int(str(a.batch).split(",")[0]), min(a.context, 4096),
-                                 min(a.steps, 64), max(3, min(a.warmup, 8)))))
+                                 min(a.steps, 64), max(3, min(a.warmup, 8)), a.compare)))
         return 0
     try:
         batches = [int(b) for b in str(a.batch).split(",") if b.strip()]

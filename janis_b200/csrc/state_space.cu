@@ -19,6 +19,13 @@ namespace janis {
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
+// A state that remembers hundreds of tokens is multiplied by decays just below 1, where a float holds exp(x) to
+// 6e-8 only and an error of one sign in every step adds up over the steps.  So the decay is kept as exp(x) - 1, which
+// expm1f gives to its own last bit however small it is, and the step is S + (S (exp(x) - 1) + input): the bracket is
+// small against S and its rounding does not count; what remains is the one rounding of the sum.
+__device__ __forceinline__ float decay_minus_one(float x) { return expm1f(x); }
+__device__ __forceinline__ float decayed(float S, float grow, float input) { return S + fmaf(S, grow, input); }
+
 // ---------------------------------------------------------------------------
 // convolution: a thread per (token, channel); the taps that reach back before the step come from the slot's state
 // ---------------------------------------------------------------------------
@@ -143,12 +150,14 @@ selective_scan_kernel(const T* __restrict__ u_rows, const T* __restrict__ dt_row
         for (int tt = 0; tt < TT; ++tt) {
             if (t0 + tt >= n_tok) break;                       // (uniform over the CTA)
             const float delta = softplus_f(dtv[tt] + bias), du = delta * uv[tt];
-            const float decay_h = g.a_per_state ? 0.f : expf(delta * Areg[0]);
+            const float x_h = delta * Areg[0];
+            const float grow_h = g.a_per_state ? 0.f : decay_minus_one(x_h);
             float acc = 0.f;
 #pragma unroll
             for (int k = 0; k < SPL; ++k) {
-                const float decay = g.a_per_state ? expf(delta * Areg[k]) : decay_h;
-                S[k] = fmaf(decay, S[k], du * Bv[tt][k]);
+                const float x = g.a_per_state ? delta * Areg[k] : x_h;
+                const float grow = g.a_per_state ? decay_minus_one(x) : grow_h;
+                S[k] = decayed(S[k], grow, du * Bv[tt][k]);
                 acc = fmaf(S[k], Cv[tt][k], acc);
             }
             for (int off = LN >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);

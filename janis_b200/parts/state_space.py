@@ -48,7 +48,7 @@ class SelectiveScanMixer(Mixer):
         self.hidden, self.inner, self.state, self.dt_rank, self.taps = hidden, inner, state, dt_rank, taps
         self.names = dict(names)
         self.init_std = init_std
-        self.w_in = self.w_conv = self.b_conv = self.w_x_lo = self.w_x_bc = self.w_dt = self.b_dt = None
+        self.w_in = self.w_conv = self.b_conv = self.w_x = self.w_dt = self.b_dt = None
         self.A = self.D = self.w_o = None
 
     def tensor_specs(self):
@@ -70,11 +70,14 @@ class SelectiveScanMixer(Mixer):
         f32 = lambda k: store.get(n[k]).to(torch.float32).contiguous()
         self.w_in = store.get(n["in"], rt.dtype).contiguous()
         self.w_conv, self.b_conv = f32("conv"), f32("conv_bias")
-        w_x = store.get(n["x"], rt.dtype)
-        self.w_x_lo, self.w_x_bc = w_x[:R].contiguous(), w_x[R:].contiguous()      # the low-rank step sizes; B | C
-        del w_x
-        store.drop(n["x"])
-        self.w_dt = store.get(n["dt"], rt.dtype).contiguous()
+        self.w_x = store.get(n["x"], rt.dtype).contiguous()                    # rows lo | B | C
+        # W_dt reads the first R columns of W_x's output; widened with zero columns it reads the whole row, so that
+        # the row needs no copy (a product with zero adds exactly nothing)
+        w_dt = store.get(n["dt"], rt.dtype)
+        self.w_dt = torch.cat([w_dt, torch.zeros((self.inner, 2 * self.state), dtype=w_dt.dtype, device=w_dt.device)],
+                              dim=1).contiguous()
+        del w_dt
+        store.drop(n["dt"])
         self.b_dt = f32("dt_bias")
         self.A = (-torch.exp(f32("A_log"))).contiguous()
         self.D = f32("D")
@@ -90,11 +93,10 @@ class SelectiveScanMixer(Mixer):
         u = ws.buf("ssm.u", (T, C), rt.dtype)
         ops.causal_conv_silu(uz, 0, C, self.w_conv, self.b_conv, cv.data, ctx.tok_seq, ctx.seq_slot, ctx.seq_first_row,
                              ctx.seq_start, ctx.seq_end, ctx.n_seq, u)
-        lo = rt.linear(u, self.w_x_lo, ws.buf("ssm.lo", (T, R), rt.dtype))
-        bc = rt.linear(u, self.w_x_bc, ws.buf("ssm.bc", (T, 2 * N), rt.dtype))
-        dt = rt.linear(lo, self.w_dt, ws.buf("ssm.dt", (T, C), rt.dtype))
+        xp = rt.linear(u, self.w_x, ws.buf("ssm.x", (T, R + 2 * N), rt.dtype))          # lo | B | C
+        dt = rt.linear(xp, self.w_dt, ws.buf("ssm.dt", (T, C), rt.dtype))
         y = ws.buf("ssm.y", (T, C), rt.dtype)
-        ops.selective_scan(u, 0, dt, 0, self.b_dt, self.A, True, bc, 0, N, self.D, uz, C, ctx.seq_slot,
+        ops.selective_scan(u, 0, dt, 0, self.b_dt, self.A, True, xp, R, R + N, self.D, uz, C, ctx.seq_slot,
                            ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, st.data, y, C, N, 1, C)
         return rt.linear(y, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))
 

@@ -10,8 +10,9 @@ are far from uniform and a key that is wrongly seen or missed changes the logits
 
 Engine cases run on the GPU (`-m gpu`, float32 and bfloat16) and, as a check of the host side alone, on the CPU
 over the plain kernel statements (float32, shorter requests).  The bfloat16 cases use folders whose routers are
-steep (scores near 0 or 1) and whose corrections are well apart: the rounding of the router's input then cannot
-change which experts are chosen, which in the soft-router folders it does for a token in a hundred.
+steep (scores at 0 or 1 for all but a token in a hundred) and whose corrections are well apart: the rounding of the
+router's input then seldom changes which experts are chosen, which in the soft-router folders it does for a token
+in a hundred, and a changed choice is a changed row of logits, not a rounding.
 """
 from __future__ import annotations
 
@@ -31,15 +32,17 @@ CASES = [pytest.param("cuda", "float32", marks=GPU), pytest.param("cuda", "bfloa
 
 def assert_logits(got, want, dtype, what):
     """float32: every logit within 1e-4 of the largest one.  bfloat16: rows are judged by the root mean square of
-    their difference against that of the logits: 98 in 100 (or all but two) within 4 %, at most one beyond 10 %."""
+    their difference against that of the logits: 98 in 100 (or all but two) within 4 %, at most two beyond 10 % (a
+    router's close call that the rounding decides the other way), half of them within 1 %."""
     if dtype in ("float32", torch.float32):
         return _assert_exact(got, want, dtype, what)
     got, want = got.detach().double().cpu(), want.double().cpu()
     assert got.shape == want.shape and torch.isfinite(got).all(), what
     rows = (got - want).pow(2).mean(1).sqrt() / want.pow(2).mean().sqrt()
     over = int((rows > 4e-2).sum())
-    assert int((rows > 1e-1).sum()) <= 1 and over <= max(2, rows.numel() // 50), \
-        f"{what}: worst row {rows.max().item():.3f} at {int(rows.argmax())}, {over} of {rows.numel()} rows over 4 %"
+    assert int((rows > 1e-1).sum()) <= 2 and over <= max(2, rows.numel() // 50) and rows.median().item() < 1e-2, \
+        (f"{what}: worst row {rows.max().item():.3f} at {int(rows.argmax())}, {over} of {rows.numel()} rows over 4 %: "
+         f"{(rows > 4e-2).nonzero().flatten().tolist()[:12]}, median {rows.median().item():.4f}")
 
 
 def _scan(inner, state, dt_rank, conv):
@@ -111,10 +114,11 @@ def write_nosolix(model_dir: str, raw: dict, seed: int, steep_router: bool = Fal
         elif name.endswith(".dt.b") or name.endswith(".dt_bias"):
             tensors[name] = (t.float() * 2.0 - 1.0).to(torch.bfloat16)
         elif name.endswith(".mlp.router"):
-            tensors[name] = (t.float() * (400.0 if steep_router else 20.0)).to(torch.bfloat16)
+            tensors[name] = (t.float() * (4000.0 if steep_router else 20.0)).to(torch.bfloat16)
         elif name.endswith(".mlp.correction") and steep_router:
             g = torch.Generator().manual_seed(seed)
-            tensors[name] = (0.06 * torch.randperm(t.numel(), generator=g).float()).to(torch.bfloat16)
+            n = t.numel()       # distinct steps with a jitter, so that sums of two do not tie between groups
+            tensors[name] = (0.07 * torch.randperm(n, generator=g).float() + 0.03 * torch.rand(n, generator=g)).to(torch.bfloat16)
         elif any(name.endswith(x) for x in (".o", ".down", ".up", ".gate", ".in", ".left.v", ".left.g", ".mix.x")):
             tensors[name] = (t.float() * 4.0).to(torch.bfloat16)
     write_model_folder(model_dir, cfg.to_dict(), tensors, {"seed": str(seed)})
