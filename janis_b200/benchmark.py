@@ -513,7 +513,7 @@ def nosolix_like(gemma: dict, layers: int) -> dict:
     scan = {"inner": 2 * W, "state": 16, "dt_rank": max(8, W // 16), "conv": 4}
     e_ff = max(8, ff // 4 // 8 * 8)
     moe = {"kind": "moe", "expert": {"ff": e_ff, "limit": 7.0}, "shared": {"ff": e_ff, "limit": 7.0},
-           "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+           "router": {"experts": 16, "top": 4, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
     out = []
     for i in range(layers):
         mixer = {"left": dict(left), "right": dict(right)} if i % 2 == 0 else dict(scan)
