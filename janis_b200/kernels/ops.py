@@ -143,8 +143,10 @@ def mixers():
         lib.janis_talk_attention_set_kernel.restype = None
         lib.janis_gla_scan.argtypes = [P, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, I, I, I, I, F, F, P]
         lib.janis_head_norm_gate.argtypes = [P, P, I, I, I, P, F, P, I, I, I, P]
-        lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, P, P]
-        lib.janis_selective_scan.argtypes = [P, I, I, I, P, I, I, P, P, I, P, I, I, I, P, P, I, I, P, P, P, P, I, P, P, I, I, I, I, P]
+        lib.janis_causal_conv_silu.argtypes = [P, I, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P, P]
+        lib.janis_selective_scan.argtypes = [P, I, I, I, P, I, I, P, P, I, P, I, I, I, P, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, P, P]
+        lib.janis_selective_scan_set_lanes.argtypes = [I]
+        lib.janis_selective_scan_set_lanes.restype = None
         lib.janis_gate_group_norm.argtypes = [P, P, I, I, I, P, F, I, P, I, I, P]
         lib.janis_dyt_norm.argtypes = [P, P, I, P, F, P, P, P, I, I, I, P]
         lib.janis_rmsnorm_accumulate.argtypes = [P, I, P, F, F, P, I, I, I, P]
@@ -908,11 +910,13 @@ def dyt_norm(h, res, alpha: float, weight, bias, out, rows=None):
 
 
 def causal_conv_silu(rows, col_off: int, channels: int, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start,
-                     seq_end, n_seq: int, out):
+                     seq_end, n_seq: int, out, one_token: bool = False):
     """out[t, c] = silu(bias[c] + sum_j weight[c, K-1-j] x[t-j, c]) over the channels rows[:, col_off : col_off +
     channels] of each sequence's tokens; inputs before the step come from state float32 [slots, max(K-1, 1), channels]
-    (the last K-1 inputs of each slot), which a second kernel then brings up to date.  Sequences without a slot
-    start from zeros and store nothing.  weight float32 [channels, K], bias float32 [channels]."""
+    (the last K-1 inputs of each slot), which is brought up to date: by the same kernel for sequences that bring one
+    token, by a second kernel for the others (one_token=True: every sequence brings one, a decode step, and the
+    second kernel is not launched).  Sequences without a slot start from zeros and store nothing.  weight float32
+    [channels, K], bias float32 [channels]."""
     T, width = rows.shape
     K = weight.shape[1]
     _t(rows, "rows", _FLOATS, (T, None))
@@ -927,20 +931,23 @@ def causal_conv_silu(rows, col_off: int, channels: int, weight, bias, state, tok
                                            _t(weight, "weight", torch.float32, (channels, K)),
                                            _t(bias, "bias", torch.float32, (channels,)), state.data_ptr(),
                                            tok_seq.data_ptr(), seq_slot.data_ptr(), seq_first_row.data_ptr(),
-                                           seq_start.data_ptr(), seq_end.data_ptr(), T, n_seq,
-                                           _t(out, "out", rows.dtype, (T, channels)), _stream()), kernels=2 if K > 1 else 1)
+                                           seq_start.data_ptr(), seq_end.data_ptr(), T, n_seq, 1 if one_token else 0,
+                                           _t(out, "out", rows.dtype, (T, channels)), _stream()),
+           kernels=2 if K > 1 and not one_token else 1)
     return out
 
 
 def selective_scan(u, u_off: int, dt, dt_off: int, dt_bias, A, a_per_state: bool, bc, b_off: int, c_off: int, D, z,
                    z_off: int, seq_slot, seq_first_row, seq_start, seq_end, n_seq: int, state, out, C: int, N: int,
-                   ch_per_head: int, ch_per_group: int):
+                   ch_per_head: int, ch_per_group: int, scratch=None):
     """The recurrence S[c, n] <- exp(delta A) S[c, n] + delta u[c] B[n], o[c] = sum_n S[c, n] C[n] + D u[c] over the
     tokens each sequence brings, in order, with delta = softplus(dt + dt_bias).  u [T, *] holds the channels at
     u_off; dt [T, *] one step size per head (c // ch_per_head) at dt_off; bc [T, *] holds B at b_off and C at c_off,
     N numbers per group (c // ch_per_group); A float32 is [heads, N] (a_per_state) or [heads]; dt_bias, D float32
     [heads].  With z ([T, *], the gate's channels at z_off) out [T, C] takes o * silu(z) in the activations' type;
-    without, out is float32 o.  state float32 [slots, C, N] is read and written back for slots >= 0."""
+    without, out is float32 o.  state float32 [slots, C, N] is read and written back for slots >= 0.  A first kernel
+    forms delta (and, with one A per head, exp(delta A) - 1) once per (token, head) into scratch (float32, at least
+    `selective_scan_scratch_floats`; allocated here when not given)."""
     T = u.shape[0]
     heads = C // ch_per_head
     dtype = u.dtype
@@ -958,14 +965,30 @@ def selective_scan(u, u_off: int, dt, dt_off: int, dt_bias, A, a_per_state: bool
         _t(tab, name, torch.int32)
         if tab.numel() < n_seq:
             raise KernelError(f"selective_scan: {name} shorter than the step's sequences")
+    need = selective_scan_scratch_floats(T, heads)
+    if scratch is None:
+        scratch = torch.empty((need,), dtype=torch.float32, device=u.device)
+    _t(scratch, "scratch", torch.float32)
+    if scratch.numel() < need:
+        raise KernelError(f"selective_scan: scratch of {scratch.numel()} floats, {need} wanted")
     lib = mixers()
     _check(lib, lib.janis_selective_scan(
         u.data_ptr(), _DT[dtype], u.shape[1], int(u_off), dt.data_ptr(), dt.shape[1], int(dt_off), dt_bias.data_ptr(),
         A.data_ptr(), 1 if a_per_state else 0, bc.data_ptr(), bc.shape[1], int(b_off), int(c_off), D.data_ptr(),
         z.data_ptr() if z is not None else None, z.shape[1] if z is not None else 0, int(z_off), seq_slot.data_ptr(),
         seq_first_row.data_ptr(), seq_start.data_ptr(), seq_end.data_ptr(), n_seq, state.data_ptr(), out.data_ptr(),
-        C, N, int(ch_per_head), int(ch_per_group), _stream()))
+        C, N, int(ch_per_head), int(ch_per_group), T, scratch.data_ptr(), _stream()), kernels=2)
     return out
+
+
+def selective_scan_scratch_floats(n_tok: int, heads: int) -> int:
+    return 2 * n_tok * heads
+
+
+def selective_scan_set_lanes(lanes: int = 0) -> None:
+    """Fix how many lanes share a channel in `selective_scan` (4, 8, 16 or 32; 0: chosen per launch, the default).
+    For tests and tuning."""
+    mixers().janis_selective_scan_set_lanes(int(lanes))
 
 
 def gate_group_norm(o, rows, z_off: int, weight, eps: float, n_groups: int, out):

@@ -92,12 +92,13 @@ class SelectiveScanMixer(Mixer):
         uz = rt.linear(x, self.w_in, ws.buf("ssm.in", (T, 2 * C), rt.dtype))
         u = ws.buf("ssm.u", (T, C), rt.dtype)
         ops.causal_conv_silu(uz, 0, C, self.w_conv, self.b_conv, cv.data, ctx.tok_seq, ctx.seq_slot, ctx.seq_first_row,
-                             ctx.seq_start, ctx.seq_end, ctx.n_seq, u)
+                             ctx.seq_start, ctx.seq_end, ctx.n_seq, u, one_token=ctx.mode == "decode")
         xp = rt.linear(u, self.w_x, ws.buf("ssm.x", (T, R + 2 * N), rt.dtype))          # lo | B | C
         dt = rt.linear(xp, self.w_dt, ws.buf("ssm.dt", (T, C), rt.dtype))
         y = ws.buf("ssm.y", (T, C), rt.dtype)
         ops.selective_scan(u, 0, dt, 0, self.b_dt, self.A, True, xp, R, R + N, self.D, uz, C, ctx.seq_slot,
-                           ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, st.data, y, C, N, 1, C)
+                           ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, st.data, y, C, N, 1, C,
+                           scratch=ws.buf("scan.steps", (ops.selective_scan_scratch_floats(T, C),), torch.float32))
         return rt.linear(y, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))
 
 
@@ -162,11 +163,11 @@ class DualityMixer(Mixer):
         rows = rt.linear(x, self.w_in, ws.buf("ssd.in", (T, C + CC + H), rt.dtype))        # z | u | B | C | dt
         ubc = ws.buf("ssd.ubc", (T, CC), rt.dtype)
         ops.causal_conv_silu(rows, C, CC, self.w_conv, self.b_conv, cv.data, ctx.tok_seq, ctx.seq_slot,
-                             ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, ubc)
+                             ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, ubc, one_token=ctx.mode == "decode")
         o = ws.buf("ssd.o", (T, C), torch.float32)
         ops.selective_scan(ubc, 0, rows, C + CC, self.b_dt, self.A, False, ubc, C, C + G * N, self.D, None, 0,
                            ctx.seq_slot, ctx.seq_first_row, ctx.seq_start, ctx.seq_end, ctx.n_seq, st.data, o, C, N, P,
-                           (H // G) * P)
+                           (H // G) * P, scratch=ws.buf("scan.steps", (ops.selective_scan_scratch_floats(T, H),), torch.float32))
         y = ws.buf("ssd.y", (T, C), rt.dtype)
         ops.gate_group_norm(o, rows, 0, self.w_norm, self.norm_eps, self.norm_groups, y)
         return rt.linear(y, self.w_o, ws.buf("mixer.out", (T, self.hidden), rt.dtype))

@@ -431,7 +431,7 @@ def dyt_norm(h, res, alpha, weight, bias, out, rows=None):
 
 
 def causal_conv_silu(rows, col_off, channels, weight, bias, state, tok_seq, seq_slot, seq_first_row, seq_start, seq_end,
-                     n_seq, out):
+                     n_seq, out, one_token=False):
     taps = weight.shape[1]
     w, b = weight.double(), bias.double()
     for s in range(n_seq):
@@ -451,7 +451,7 @@ def causal_conv_silu(rows, col_off, channels, weight, bias, state, tok_seq, seq_
 
 
 def selective_scan(u, u_off, dt, dt_off, dt_bias, A, a_per_state, bc, b_off, c_off, D, z, z_off, seq_slot, seq_first_row,
-                   seq_start, seq_end, n_seq, state, out, C, N, ch_per_head, ch_per_group):
+                   seq_start, seq_end, n_seq, state, out, C, N, ch_per_head, ch_per_group, scratch=None):
     heads = C // ch_per_head
     Af = A.double() if a_per_state else A.double()[:, None].expand(heads, N)
     Ac = Af.repeat_interleave(ch_per_head, dim=0)                           # [C, N]
@@ -477,6 +477,10 @@ def selective_scan(u, u_off, dt, dt_off, dt_bias, A, a_per_state, bc, b_off, c_o
         if slot >= 0:
             state[slot] = S.float()
     return out
+
+
+def selective_scan_scratch_floats(n_tok, heads):
+    return 2 * n_tok * heads
 
 
 def gate_group_norm(o, rows, z_off, weight, eps, n_groups, out):

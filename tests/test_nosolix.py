@@ -292,6 +292,17 @@ def test_conv_kernel_against_its_statement(dtype, C, K, off, width):
                          seq_start.cuda(), seq_end.cuda(), len(lens), got)
     _close(got, want, dtype, "conv")
     assert torch.equal(got_state.cpu(), want_state), "the inputs kept for the next step"
+    # a decode step: one token a sequence, the kept inputs shifted by the convolution's own kernel
+    lens, starts, slots = [1, 1, 1, 1], [0, 9, 2, 5], [5, 3, -1, 0]
+    tok_seq, seq_slot, first, seq_start, seq_end, T = _tables(lens, starts, slots)
+    rows = torch.randn(T, width, generator=g).to(dtype)
+    want, want_state = torch.zeros(T, C, dtype=dtype), state.clone()
+    R.causal_conv_silu(rows, off, C, w, b, want_state, tok_seq, seq_slot, first, seq_start, seq_end, len(lens), want)
+    got, got_state = torch.full((T, C), float("nan"), dtype=dtype, device="cuda"), state.clone().cuda()
+    ops.causal_conv_silu(rows.cuda(), off, C, w.cuda(), b.cuda(), got_state, tok_seq.cuda(), seq_slot.cuda(), first.cuda(),
+                         seq_start.cuda(), seq_end.cuda(), len(lens), got, one_token=True)
+    _close(got, want, dtype, "conv, one token a sequence")
+    assert torch.equal(got_state.cpu(), want_state), "the inputs kept after a decode step"
 
 
 @GPU
@@ -322,11 +333,18 @@ def test_scan_kernel_against_its_statement(dtype, C, N, cph, cpg, per_state, gat
                                  dev(z) if gated else None, 2, dev(seq_slot), dev(first), dev(seq_start), dev(seq_end),
                                  len(lens), st, out, C, N, cph, cpg)
     R.selective_scan(*args(lambda x: x, want_state, want))
-    got, got_state = torch.full((T, C), float("nan"), dtype=out_dtype, device="cuda"), state.clone().cuda()
-    ops.selective_scan(*args(lambda x: x.cuda(), got_state, got))
-    _close(got, want, out_dtype, "scan", f32=5e-5)
-    _close(got_state, want_state, torch.float32, "the state left behind", f32=5e-5)
-    assert torch.equal(got_state[2].cpu(), state[2]), "a slot that is not in the step keeps its state"
+    for lanes in (0, 4, 8, 16, 32):                    # chosen by the launch, then every count that holds the states
+        if lanes and lanes * 16 < N:
+            continue
+        ops.selective_scan_set_lanes(lanes)
+        try:
+            got, got_state = torch.full((T, C), float("nan"), dtype=out_dtype, device="cuda"), state.clone().cuda()
+            ops.selective_scan(*args(lambda x: x.cuda(), got_state, got))
+        finally:
+            ops.selective_scan_set_lanes(0)
+        _close(got, want, out_dtype, f"scan, {lanes} lanes", f32=5e-5)
+        _close(got_state, want_state, torch.float32, "the state left behind", f32=5e-5)
+        assert torch.equal(got_state[2].cpu(), state[2]), "a slot that is not in the step keeps its state"
 
 
 @GPU
