@@ -182,7 +182,7 @@ selective_scan_kernel(const T* __restrict__ u_rows, const T* __restrict__ bc_row
                       const float* __restrict__ D, ScanShape g, const int* __restrict__ seq_slot,
                       const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
                       const int* __restrict__ seq_end, float* __restrict__ state, void* __restrict__ out_raw) {
-    constexpr int TT = SPL <= 2 ? 8 : (SPL <= 4 ? 4 : 2);
+    constexpr int TT = SPL <= 2 ? 8 : (SPL <= 4 ? 4 : 2);          // tokens whose inputs are asked for together (deeper tiles measured slower)
     const int LN = g.ln, N = g.N, C = g.C;
     const int seq = blockIdx.x, tid = threadIdx.x, l = tid & (LN - 1), n0 = l * SPL;
     const int c_raw = blockIdx.y * (SCAN_THREADS / LN) + tid / LN;
