@@ -281,6 +281,150 @@ selective_scan_kernel(const T* __restrict__ u_rows, const T* __restrict__ bc_row
     }
 }
 
+// The prompt form.  A token costs a channel's lanes little arithmetic, so the other form spends its time waiting
+// for each token's inputs.  Here the B and C rows of a tile of 16 tokens, which every channel of the CTA reads, are
+// copied into shared memory once (cp.async, 16 bytes a piece, the next tile's on their way while this one is
+// computed: two buffers), and the tile's step sizes, inputs and gates, gathered per (token, channel), pass through
+// registers a tile ahead and then through shared memory.  Conditions (the launcher checks them): the CTA's channels
+// lie in one group of B and C, rows of B and C are whole 16-byte pieces at 16-byte offsets, no CTA is partly empty.
+constexpr int SCAN_TS = 16;
+
+__device__ __forceinline__ void scan_cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
+template <typename T, int SPL, bool PER_STATE, bool VEC>
+__global__ void __launch_bounds__(SCAN_THREADS)
+selective_scan_staged_kernel(const T* __restrict__ u_rows, const T* __restrict__ bc_rows, const T* __restrict__ z_rows,
+                             const float* __restrict__ delta, const float* __restrict__ grow, const float* __restrict__ A,
+                             const float* __restrict__ D, ScanShape g, const int* __restrict__ seq_slot,
+                             const int* __restrict__ seq_first_row, const int* __restrict__ seq_start,
+                             const int* __restrict__ seq_end, float* __restrict__ state, void* __restrict__ out_raw) {
+    extern __shared__ __align__(16) unsigned char scan_smem[];
+    constexpr int TS = SCAN_TS, EPP = 16 / (int)sizeof(T);          // elements a 16-byte piece
+    const int LN = g.ln, N = g.N, C = g.C, CPC = SCAN_THREADS / LN;
+    T* bc_s = reinterpret_cast<T*>(scan_smem);                       // [2][TS][2][N]: a token's B, then its C
+    float* sc_s = reinterpret_cast<float*>(scan_smem + (size_t)2 * TS * 2 * N * sizeof(T));      // [4][TS][CPC]: delta, grow, u, z
+    const int seq = blockIdx.x, tid = threadIdx.x, l = tid & (LN - 1), n0 = l * SPL, j = tid / LN;
+    const int c0 = blockIdx.y * CPC, c = c0 + j;
+    const int head = c / g.cph, group = c0 / g.cpg;
+    const bool whole = n0 + SPL <= N, gated = g.gated != 0;
+    grid_dependents_launch();
+    const int slot = seq_slot[seq], row0 = seq_first_row[seq], n_tok = seq_end[seq] - seq_start[seq];
+    if (n_tok <= 0) return;
+    const float Dh = D[head];
+    float Areg[SPL];
+#pragma unroll
+    for (int k = 0; k < SPL; ++k) Areg[k] = (PER_STATE && n0 + k < N) ? A[(size_t)head * N + n0 + k] : 0.f;
+    grid_dependency_wait();
+    float S[SPL];
+    float* st = slot >= 0 ? state + ((size_t)slot * C + c) * N : nullptr;
+#pragma unroll
+    for (int k = 0; k < SPL; ++k) S[k] = (st != nullptr && n0 + k < N) ? st[n0 + k] : 0.f;
+    const int pieces = N / EPP;                                      // 16-byte pieces of a row of B (and of C)
+    const T* bsrc = bc_rows + (size_t)row0 * g.bc_stride + g.b_off + group * N;
+    const int c_from_b = g.c_off - g.b_off;
+    auto issue_bc = [&](int t0, int buf) {
+        for (int p = tid; p < TS * 2 * pieces; p += SCAN_THREADS) {
+            const int tt = p / (2 * pieces), q = p - tt * 2 * pieces, which = q >= pieces ? 1 : 0, i = q - which * pieces;
+            const unsigned r = (unsigned)min(t0 + tt, n_tok - 1);
+            scan_cp_async16(bc_s + ((size_t)(buf * TS + tt) * 2 + which) * N + i * EPP,
+                            bsrc + (size_t)r * g.bc_stride + (which ? c_from_b : 0) + i * EPP);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    // the tile's scalars: element e = tid + i 128 is (token e / CPC, channel c0 + e % CPC)
+    constexpr int SC = 4;                                            // TS CPC / 128 <= 4
+    float sd[SC], sg[SC], su[SC], sz[SC];
+    auto fetch_scalars = [&](int t0) {
+#pragma unroll
+        for (int i = 0; i < SC; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            sd[i] = sg[i] = su[i] = sz[i] = 0.f;
+            if (e < TS * CPC) {
+                const int tt = e / CPC, ch = c0 + e - tt * CPC;
+                const size_t row = (size_t)(row0 + min(t0 + tt, n_tok - 1));
+                const int h = ch / g.cph;
+                sd[i] = delta[row * g.heads + h];
+                if (!PER_STATE) sg[i] = grow[row * g.heads + h];
+                su[i] = to_float(u_rows[row * g.u_stride + g.u_off + ch]);
+                if (gated) sz[i] = to_float(z_rows[row * g.z_stride + g.z_off + ch]);
+            }
+        }
+    };
+    issue_bc(0, 0);
+    fetch_scalars(0);
+    T* out_t = reinterpret_cast<T*>(out_raw) + (size_t)row0 * C + c;
+    float* out_f = reinterpret_cast<float*>(out_raw) + (size_t)row0 * C + c;
+    int buf = 0;
+    for (int t0 = 0; t0 < n_tok; t0 += TS, buf ^= 1) {
+        __syncthreads();                                             // the tile before has been read
+#pragma unroll
+        for (int i = 0; i < SC; ++i) {
+            const int e = tid + i * SCAN_THREADS;
+            if (e < TS * CPC) {
+                sc_s[e] = sd[i];
+                sc_s[TS * CPC + e] = sg[i];
+                sc_s[2 * TS * CPC + e] = su[i];
+                sc_s[3 * TS * CPC + e] = sz[i];
+            }
+        }
+        const bool more = t0 + TS < n_tok;
+        if (more) {
+            issue_bc(t0 + TS, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        }
+        __syncthreads();
+        if (more) fetch_scalars(t0 + TS);
+        const int tt_n = min(TS, n_tok - t0);
+        for (int tt = 0; tt < tt_n; ++tt) {
+            const float dl = sc_s[tt * CPC + j], grh = sc_s[TS * CPC + tt * CPC + j], uu = sc_s[2 * TS * CPC + tt * CPC + j];
+            const float du = dl * uu;
+            float Bv[SPL], Cv[SPL];
+            const T* brow = bc_s + ((size_t)(buf * TS + tt) * 2) * N + n0;
+            if (VEC) {
+                if (whole) {
+                    load_run<T, SPL, VEC>(brow, Bv);
+                    load_run<T, SPL, VEC>(brow + N, Cv);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < SPL; ++k) Bv[k] = Cv[k] = 0.f;
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < SPL; ++k) {
+                    const bool in = n0 + k < N;
+                    Bv[k] = in ? to_float(brow[k]) : 0.f;
+                    Cv[k] = in ? to_float(brow[N + k]) : 0.f;
+                }
+            }
+            float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+            for (int k = 0; k < SPL; ++k) {
+                const float gr = PER_STATE ? decay_minus_one(dl * Areg[k]) : grh;
+                S[k] = decayed(S[k], gr, du * Bv[k]);
+                if (k & 1) acc1 = fmaf(S[k], Cv[k], acc1);
+                else acc0 = fmaf(S[k], Cv[k], acc0);
+            }
+            float acc = acc0 + acc1;
+            for (int off = LN >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (l == 0) {
+                const float y = fmaf(Dh, uu, acc);
+                const size_t at = (size_t)(unsigned)(t0 + tt) * C;
+                if (gated) out_t[at] = from_float<T>(y * silu_f(sc_s[3 * TS * CPC + tt * CPC + j]));
+                else out_f[at] = y;
+            }
+        }
+    }
+    if (st != nullptr) {
+#pragma unroll
+        for (int k = 0; k < SPL; ++k)
+            if (n0 + k < N) st[n0 + k] = S[k];
+    }
+}
+
 // y[t, part] = x / sqrt(mean(x^2) + eps) * w with x = o * silu(z): a CTA per (token, part)
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -343,10 +487,40 @@ JANIS_EXPORT int janis_causal_conv_silu(const void* rows, int dtype, int row_ele
 
 template <typename T, bool PER_STATE>
 static int scan_launch(const void* u, const void* bc, const void* z, const float* delta, const float* grow, const float* A,
-                       const float* D, ScanShape g, int spl, bool vec, const int* seq_slot, const int* seq_first_row,
-                       const int* seq_start, const int* seq_end, int n_seq, float* state, void* out, cudaStream_t stream) {
+                       const float* D, ScanShape g, int spl, bool vec, size_t staged_bytes, const int* seq_slot,
+                       const int* seq_first_row, const int* seq_start, const int* seq_end, int n_seq, float* state, void* out,
+                       cudaStream_t stream) {
     const int per_cta = SCAN_THREADS / g.ln;
     const dim3 grid(n_seq, (g.C + per_cta - 1) / per_cta), block(SCAN_THREADS);
+    if (staged_bytes > 0) {
+#define JANIS_SCAN_STAGED(SPL, VEC)                                                                                    \
+    {                                                                                                                  \
+        static size_t most = 0;                                                                                        \
+        if (staged_bytes > most) {                                                                                     \
+            cudaError_t e = cudaFuncSetAttribute(selective_scan_staged_kernel<T, SPL, PER_STATE, VEC>,                 \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged_bytes);      \
+            if (e != cudaSuccess) return fail("selective_scan: shared memory of %zu bytes refused: %s", staged_bytes, cudaGetErrorString(e)); \
+            most = staged_bytes;                                                                                       \
+        }                                                                                                              \
+        return launch_kernel("selective_scan", selective_scan_staged_kernel<T, SPL, PER_STATE, VEC>, grid, block,      \
+                             staged_bytes, stream, 1, (const T*)u, (const T*)bc, (const T*)z, delta, grow, A, D, g,     \
+                             seq_slot, seq_first_row, seq_start, seq_end, state, out);                                  \
+    }
+        if (vec) {
+            if (spl == 2) JANIS_SCAN_STAGED(2, true)
+            if (spl == 4) JANIS_SCAN_STAGED(4, true)
+            if (spl == 8) JANIS_SCAN_STAGED(8, true)
+            if (spl == 16) JANIS_SCAN_STAGED(16, true)
+        }
+        if (spl <= 1) JANIS_SCAN_STAGED(1, false)
+        if (spl <= 2) JANIS_SCAN_STAGED(2, false)
+        if (spl <= 3) JANIS_SCAN_STAGED(3, false)
+        if (spl <= 4) JANIS_SCAN_STAGED(4, false)
+        if (spl <= 6) JANIS_SCAN_STAGED(6, false)
+        if (spl <= 8) JANIS_SCAN_STAGED(8, false)
+        if (spl <= 16) JANIS_SCAN_STAGED(16, false)
+#undef JANIS_SCAN_STAGED
+    }
 #define JANIS_SCAN_LAUNCH(SPL, VEC)                                                                                    \
     return launch_kernel("selective_scan", selective_scan_kernel<T, SPL, PER_STATE, VEC>, grid, block, 0, stream, 1,    \
                          (const T*)u, (const T*)bc, (const T*)z, delta, grow, A, D, g, seq_slot, seq_first_row,          \
@@ -373,6 +547,10 @@ JANIS_EXPORT long long janis_selective_scan_scratch(int n_tok, int heads) { retu
 static int scan_lanes_forced = 0;      // lanes a channel fixed by a test or a tuning run (0: chosen per launch)
 
 JANIS_EXPORT void janis_selective_scan_set_lanes(int lanes) { scan_lanes_forced = lanes; }
+
+static int scan_form_forced = 0;       // 0: the prompt form with its tiles in shared memory where it fits and pays; 1: never; 2: wherever it fits (tests)
+
+JANIS_EXPORT void janis_selective_scan_set_form(int form) { scan_form_forced = form; }
 
 JANIS_EXPORT int janis_selective_scan(const void* u, int dtype, int u_stride, int u_off, const void* dt, int dt_stride,
                                       int dt_off, const float* dt_bias, const float* A, int a_per_state, const void* bc,
@@ -427,6 +605,19 @@ JANIS_EXPORT int janis_selective_scan(const void* u, int dtype, int u_stride, in
     const bool vec = (best_spl == 2 || best_spl == 4 || best_spl == 8 || best_spl == 16) && N % best_spl == 0 && b_off % best_spl == 0 &&
                      c_off % best_spl == 0 && bc_stride % best_spl == 0 && ((uintptr_t)bc % run) == 0 &&
                      ((size_t)bc_stride * esz) % run == 0 && ((size_t)b_off * esz) % run == 0 && ((size_t)c_off * esz) % run == 0;
+    // the prompt form where its conditions hold (see the kernel): 0 bytes means the other form
+    size_t staged_bytes = 0;
+    {
+        const int cpc = SCAN_THREADS / best_ln;
+        const size_t row_bytes = (size_t)N * esz;
+        // (with few states a token's rows are small and the tile's two barriers cost more than the copies save: 4,608
+        // channels, 2,048 tokens, 16 states 1.6 ms against 1.0 in the other form; 128 states 0.96 against 1.28)
+        const bool fits = n_tok > n_seq && scan_form_forced != 1 && (N >= 64 || scan_form_forced == 2) && C % cpc == 0 && cpg % cpc == 0 && row_bytes % 16 == 0 &&
+                          ((size_t)bc_stride * esz) % 16 == 0 && ((size_t)b_off * esz) % 16 == 0 && ((size_t)c_off * esz) % 16 == 0 &&
+                          ((uintptr_t)bc & 15) == 0 && SCAN_TS * cpc <= 4 * SCAN_THREADS;
+        const size_t bytes = (size_t)2 * SCAN_TS * 2 * row_bytes + (size_t)4 * SCAN_TS * cpc * sizeof(float);
+        if (fits && bytes <= 96 * 1024) staged_bytes = bytes;
+    }
     float* delta = scratch;
     float* grow = scratch + (size_t)n_tok * g.heads;
     const size_t n = (size_t)n_tok * g.heads, want = (n + 255) / 256;
@@ -436,15 +627,15 @@ JANIS_EXPORT int janis_selective_scan(const void* u, int dtype, int u_stride, in
         if (launch_kernel("scan_steps", scan_steps_kernel<float>, sgrid, sblock, 0, stream, 1, (const float*)dt, dt_stride, dt_off,
                           dt_bias, A_head, delta, grow, g.heads, n))
             return 1;
-        return a_per_state ? scan_launch<float, true>(u, bc, z, delta, grow, A, D, g, best_spl, vec, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream)
-                           : scan_launch<float, false>(u, bc, z, delta, grow, A, D, g, best_spl, vec, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream);
+        return a_per_state ? scan_launch<float, true>(u, bc, z, delta, grow, A, D, g, best_spl, vec, staged_bytes, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream)
+                           : scan_launch<float, false>(u, bc, z, delta, grow, A, D, g, best_spl, vec, staged_bytes, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream);
     }
     if (dtype == JANIS_BF16) {
         if (launch_kernel("scan_steps", scan_steps_kernel<bf16>, sgrid, sblock, 0, stream, 1, (const bf16*)dt, dt_stride, dt_off,
                           dt_bias, A_head, delta, grow, g.heads, n))
             return 1;
-        return a_per_state ? scan_launch<bf16, true>(u, bc, z, delta, grow, A, D, g, best_spl, vec, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream)
-                           : scan_launch<bf16, false>(u, bc, z, delta, grow, A, D, g, best_spl, vec, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream);
+        return a_per_state ? scan_launch<bf16, true>(u, bc, z, delta, grow, A, D, g, best_spl, vec, staged_bytes, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream)
+                           : scan_launch<bf16, false>(u, bc, z, delta, grow, A, D, g, best_spl, vec, staged_bytes, seq_slot, seq_first_row, seq_start, seq_end, n_seq, state, out, stream);
     }
     return fail("selective_scan: unknown dtype %d", dtype);
 }

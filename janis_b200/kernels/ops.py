@@ -147,6 +147,8 @@ def mixers():
         lib.janis_selective_scan.argtypes = [P, I, I, I, P, I, I, P, P, I, P, I, I, I, P, P, I, I, P, P, P, P, I, P, P, I, I, I, I, I, P, P]
         lib.janis_selective_scan_set_lanes.argtypes = [I]
         lib.janis_selective_scan_set_lanes.restype = None
+        lib.janis_selective_scan_set_form.argtypes = [I]
+        lib.janis_selective_scan_set_form.restype = None
         lib.janis_gate_group_norm.argtypes = [P, P, I, I, I, P, F, I, P, I, I, P]
         lib.janis_dyt_norm.argtypes = [P, P, I, P, F, P, P, P, I, I, I, P]
         lib.janis_rmsnorm_accumulate.argtypes = [P, I, P, F, F, P, I, I, I, P]
@@ -989,6 +991,13 @@ def selective_scan_set_lanes(lanes: int = 0) -> None:
     """Fix how many lanes share a channel in `selective_scan` (4, 8, 16 or 32; 0: chosen per launch, the default).
     For tests and tuning."""
     mixers().janis_selective_scan_set_lanes(int(lanes))
+
+
+def selective_scan_set_form(form: int = 0) -> None:
+    """0: a step in which a sequence brings several tokens runs the form that stages tiles of B and C in shared memory
+    where the sizes allow it and there are 64 states a channel or more (the default); 1: always the form that keeps a
+    tile's inputs in registers; 2: the staged form wherever the sizes allow it.  For tests."""
+    mixers().janis_selective_scan_set_form(int(form))
 
 
 def gate_group_norm(o, rows, z_off: int, weight, eps: float, n_groups: int, out):

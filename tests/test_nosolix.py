@@ -311,9 +311,12 @@ def test_conv_kernel_against_its_statement(dtype, C, K, off, width):
     (96, 12, 1, 96, True, True), (50, 3, 1, 50, True, True), (34, 37, 1, 34, True, True), (64, 128, 1, 64, True, True),
     (32, 12, 8, 16, False, False), (30, 7, 6, 6, False, False), (128, 128, 64, 64, False, False), (22, 5, 22, 22, False, False),
     (256, 16, 1, 256, True, True), (40, 300, 8, 20, False, False), (16, 48, 4, 16, False, True)])
-def test_scan_kernel_against_its_statement(dtype, C, N, cph, cpg, per_state, gated):
+@pytest.mark.parametrize("aligned", [False, True])
+def test_scan_kernel_against_its_statement(dtype, C, N, cph, cpg, per_state, gated, aligned):
     """Sequences from zero, from a stored state, of one token and of many, and a padding sequence; the state left
-    behind is compared too.  Step sizes are spread so that some channels forget at once and others keep all."""
+    behind is compared too.  Step sizes are spread so that some channels forget at once and others keep all.
+    `aligned` puts B and C at 16-byte offsets in rows of whole 16-byte pieces, which the form with tiles in shared
+    memory wants (it then runs where the state count allows it, and the register form is run beside it)."""
     from janis_b200.kernels import ops
     from tests import kernel_refs as R
     lens, starts, slots = [9, 1, 70, 2], [0, 30, 5, 0], [3, 0, 1, -1]
@@ -322,27 +325,30 @@ def test_scan_kernel_against_its_statement(dtype, C, N, cph, cpg, per_state, gat
     g = torch.Generator().manual_seed(C * N)
     u = torch.randn(T, C + 5, generator=g).to(dtype)
     dt = (torch.randn(T, heads + 3, generator=g) * 2.0).to(dtype)
-    bc = torch.randn(T, 2 * groups * N + 4, generator=g).to(dtype)
+    pad = 16 if aligned else 4                     # where B starts in its rows
+    bc = torch.randn(T, (2 * groups * N + pad + 7) // 8 * 8 if aligned else 2 * groups * N + pad, generator=g).to(dtype)
     z = torch.randn(T, C + 2, generator=g).to(dtype) if gated else None
     dt_bias, D = torch.randn(heads, generator=g) - 1.0, torch.randn(heads, generator=g)
     A = -torch.exp(torch.randn(heads, N, generator=g)) if per_state else -torch.exp(torch.randn(heads, generator=g))
     state = torch.randn(4, C, N, generator=g)
     out_dtype = dtype if gated else torch.float32
     want, want_state = torch.zeros(T, C, dtype=out_dtype), state.clone()
-    args = lambda dev, st, out: (dev(u), 5, dev(dt), 3, dev(dt_bias), dev(A), per_state, dev(bc), 4, 4 + groups * N, dev(D),
+    args = lambda dev, st, out: (dev(u), 5, dev(dt), 3, dev(dt_bias), dev(A), per_state, dev(bc), pad, pad + groups * N, dev(D),
                                  dev(z) if gated else None, 2, dev(seq_slot), dev(first), dev(seq_start), dev(seq_end),
                                  len(lens), st, out, C, N, cph, cpg)
     R.selective_scan(*args(lambda x: x, want_state, want))
-    for lanes in (0, 4, 8, 16, 32):                    # chosen by the launch, then every count that holds the states
-        if lanes and lanes * 16 < N:
+    for lanes, form in [(n, f) for n in (0, 4, 8, 16, 32) for f in ((2, 1) if aligned else (0,))]:
+        if lanes and lanes * 16 < N:                   # (0: chosen by the launch; then every count that holds the states)
             continue
         ops.selective_scan_set_lanes(lanes)
+        ops.selective_scan_set_form(form)
         try:
             got, got_state = torch.full((T, C), float("nan"), dtype=out_dtype, device="cuda"), state.clone().cuda()
             ops.selective_scan(*args(lambda x: x.cuda(), got_state, got))
         finally:
             ops.selective_scan_set_lanes(0)
-        _close(got, want, out_dtype, f"scan, {lanes} lanes", f32=5e-5)
+            ops.selective_scan_set_form(0)
+        _close(got, want, out_dtype, f"scan, {lanes} lanes, form {form}", f32=5e-5)
         _close(got_state, want_state, torch.float32, "the state left behind", f32=5e-5)
         assert torch.equal(got_state[2].cpu(), state[2]), "a slot that is not in the step keeps its state"
 
@@ -559,3 +565,51 @@ def test_greedy_generation_through_the_engine(engines, nos_dirs, on, dtype):
         for _ in range(n_new):
             seq.append(int(P.forward(cfg, w, seq)[-1].argmax()))
         assert r == seq[len(p):], (p, r, seq[len(p):])
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_and_command_line(nos_dirs, plain, dtype, tmp_path):
+    """`bin/trace_run` as a user runs it: the model class comes from config.json; prompts in one batch, decoded
+    together, a second batch on the freed slots; and `bin/janis generate` on the same folder."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from tests.test_generation import ROOT, _trace
+    key, steep = "D", dtype == "bfloat16"
+    V = NOS[key]["vocab"]
+    lens = [40, 9, 75, 1, 23, 130]
+    reqs = [random_tokens(V, n, 210 + n) for n in lens]
+    steps, peak = _trace(reqs, [max(1, n - 32) for n in lens], batch_of=3)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", nos_dirs[(key, steep)], "--dtype", dtype,
+                        "--out", str(out), "--max-tokens", str(peak)],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.split() == [w for s in steps for w in ("done", str(s["step"]))]
+    got = {f"r{i}": [] for i in range(len(reqs))}
+    for s in steps:
+        arr = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, V)
+        o = 0
+        for e in s["entries"]:
+            got[e["id"]].append(torch.from_numpy(arr[o:o + len(e["want"])].copy()))
+            o += len(e["want"])
+        assert o == arr.shape[0]
+    for i, r in enumerate(reqs):
+        assert_logits(torch.cat(got[f"r{i}"]), plain(key, steep, r), dtype, f"trace request {i}")
+    if dtype == "float32":
+        from tests.plain import nosolix_plain as P
+        cfg, w = P.load_folder(nos_dirs[(key, steep)])
+        prompt = reqs[1]
+        g = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "janis"), "generate", "--model", nos_dirs[(key, steep)],
+                            "--dtype", "float32", "--ids", ",".join(map(str, prompt)), "--max-tokens", "5", "--temp", "0", "--stop", ""],
+                           capture_output=True, text=True, timeout=900)
+        assert g.returncode == 0, g.stderr[-2000:]
+        seq = list(prompt)
+        for _ in range(5):
+            seq.append(int(P.forward(cfg, w, seq)[-1].argmax()))
+        assert ",".join(map(str, seq[len(prompt):])) in g.stdout.replace(" ", ""), g.stdout
