@@ -613,3 +613,28 @@ def test_trace_replay_and_command_line(nos_dirs, plain, dtype, tmp_path):
         for _ in range(5):
             seq.append(int(P.forward(cfg, w, seq)[-1].argmax()))
         assert ",".join(map(str, seq[len(prompt):])) in g.stdout.replace(" ", ""), g.stdout
+
+
+@GPU
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_shapes_of_a_real_model(tmp_path, dtype):
+    """Two layers at the layer sizes of a 2-billion-parameter model (width 2304; 8 heads over 4 of 256; 72 state-space
+    heads of 64 channels with 128 states; 4,608 scan channels with 16 states; 8 experts of 1,152), vocabulary cut to
+    2,048: the kernels' launch shapes, vector loads and staged tiles at sizes the small models do not reach.  A prompt
+    longer than the window, then decoded; beside it a short prompt."""
+    from tests.plain import nosolix_plain as P
+    raw = {"architecture": "Nosolix", "vocab": 2048, "width": 2304, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "layers": [
+        _layer("parallel", _par(8, 4, 256, 256, 256, 200, 256 ** -0.5, (72, 64, 128, 1, 1, 4), scaling=(8.0, 1.0, 4.0, 128)),
+               _moe(8, 2, 1152, 7.0, 1.5, 2, 1, shared=(1152, 7.0))),
+        _layer("mamba1", _scan(4608, 16, 144, 4), DENSE(9216))]}
+    steep = dtype == "bfloat16"
+    write_nosolix(str(tmp_path), raw, 77, steep)
+    cfg, w = P.load_folder(str(tmp_path))
+    eng = make_engine(str(tmp_path), dtype, "cuda", max_tokens=1024)
+    try:
+        reqs = _requests(2048, [300 + 8, 5 + 8], 3)
+        got = run_requests(eng, reqs, [300, 5])
+        for i, r in enumerate(reqs):
+            assert_logits(got[i], P.forward(cfg, w, r), dtype, f"real layer shapes, request {i}")
+    finally:
+        eng.close()
