@@ -100,27 +100,29 @@ NOS_D = {"architecture": "Nosolix", "vocab": 301, "width": 70, "embedding": {"sc
 NOS = {"A": NOS_A, "B": NOS_B, "C": NOS_C, "D": NOS_D}
 
 
-def write_nosolix(model_dir: str, raw: dict, seed: int, steep_router: bool = False) -> None:
+def write_nosolix(model_dir: str, raw: dict, seed: int, steep_router: bool = False, gain: float = 4.0,
+                  qk_gain: float = 6.0, router_gain: float = 20.0) -> None:
     """A folder of seeded random weights: query and key projections scaled up; step-size biases spread, so that
     some channels forget within a few tokens and others remember hundreds; with steep_router the routers' rows are
-    scaled up (scores near 0 or 1) and the corrections are distinct multiples of 0.06."""
+    scaled up (scores near 0 or 1) and the corrections are distinct steps with a jitter.  The gains suit widths of
+    a hundred; a model of real width takes smaller ones."""
     from janis_b200 import build_model
     from janis_b200.weights.loader import random_tensors, write_model_folder
     _, cfg, model = build_model(raw)
     tensors = random_tensors(model.tensor_specs(), seed, "cpu")
     for name, t in list(tensors.items()):
         if name.endswith(".left.q") or name.endswith(".left.k"):
-            tensors[name] = (t.float() * 6.0).to(torch.bfloat16)
+            tensors[name] = (t.float() * qk_gain).to(torch.bfloat16)
         elif name.endswith(".dt.b") or name.endswith(".dt_bias"):
             tensors[name] = (t.float() * 2.0 - 1.0).to(torch.bfloat16)
         elif name.endswith(".mlp.router"):
-            tensors[name] = (t.float() * (4000.0 if steep_router else 20.0)).to(torch.bfloat16)
+            tensors[name] = (t.float() * router_gain * (200.0 if steep_router else 1.0)).to(torch.bfloat16)
         elif name.endswith(".mlp.correction") and steep_router:
             g = torch.Generator().manual_seed(seed)
             n = t.numel()       # distinct steps with a jitter, so that sums of two do not tie between groups
             tensors[name] = (0.07 * torch.randperm(n, generator=g).float() + 0.03 * torch.rand(n, generator=g)).to(torch.bfloat16)
         elif any(name.endswith(x) for x in (".o", ".down", ".up", ".gate", ".in", ".left.v", ".left.g", ".mix.x")):
-            tensors[name] = (t.float() * 4.0).to(torch.bfloat16)
+            tensors[name] = (t.float() * gain).to(torch.bfloat16)
     write_model_folder(model_dir, cfg.to_dict(), tensors, {"seed": str(seed)})
 
 
@@ -628,7 +630,7 @@ def test_layer_shapes_of_a_real_model(tmp_path, dtype):
                _moe(8, 2, 1152, 7.0, 1.5, 2, 1, shared=(1152, 7.0))),
         _layer("mamba1", _scan(4608, 16, 144, 4), DENSE(9216))]}
     steep = dtype == "bfloat16"
-    write_nosolix(str(tmp_path), raw, 77, steep)
+    write_nosolix(str(tmp_path), raw, 77, steep, gain=1.0, qk_gain=2.0, router_gain=2.0)
     cfg, w = P.load_folder(str(tmp_path))
     eng = make_engine(str(tmp_path), dtype, "cuda", max_tokens=1024)
     try:
